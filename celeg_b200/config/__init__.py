@@ -12,11 +12,14 @@ from .ramosun_arch import build_ramosun_spec
 from .kedesun import KedesunConfig
 from . import kedesun_arch as _kedesun_arch  # registers "Kedesun"
 from .kedesun_arch import build_kedesun_spec
+from .naselorn import NaselornConfig
+from . import naselorn_arch as _naselorn_arch  # registers "Naselorn"
+from .naselorn_arch import build_naselorn_spec
 
 __all__ = [
     "Architecture", "ConfigError", "UnknownArchitectureError", "ExecutionEntry", "LayerSpec",
     "ModelSpec", "PartSpec", "TensorRef", "architecture_named", "architecture_of",
     "known_architectures", "read_config_json", "register_architecture", "CONV",
     "FULL_ATTENTION", "Lfm2Config", "build_lfm2_spec", "RamosunConfig", "build_ramosun_spec",
-    "KedesunConfig", "build_kedesun_spec",
+    "KedesunConfig", "build_kedesun_spec", "NaselornConfig", "build_naselorn_spec",
 ]

@@ -50,13 +50,14 @@ __device__ __forceinline__ float block_sum(float v, float* scratch) {
 }
 
 // Element-wise activations by code (the feed-forward parts name one): 0 the exact GELU (erf), 1 the tanh GELU, 2 SiLU,
-// 3 the square of ReLU.
-enum Activation : int { kGeluErf = 0, kGeluTanh = 1, kSilu = 2, kSquaredRelu = 3 };
+// 3 the square of ReLU, 4 ReLU.
+enum Activation : int { kGeluErf = 0, kGeluTanh = 1, kSilu = 2, kSquaredRelu = 3, kRelu = 4 };
 
 __device__ __forceinline__ float activate(float z, int kind) {
     if (kind == kGeluErf) return 0.5f * z * (1.0f + erff(z * 0.70710678118654752f));
     if (kind == kGeluTanh) return 0.5f * z * (1.0f + tanhf(0.79788456080286536f * (z + 0.044715f * z * z * z)));
     if (kind == kSquaredRelu) return z > 0.0f ? z * z : 0.0f;
+    if (kind == kRelu) return fmaxf(z, 0.0f);
     return z / (1.0f + expf(-z));
 }
 

@@ -150,9 +150,41 @@ CELEG_API int celeg_join_stream_embedding(const float* residual, const void* del
 }
 
 // out = act(in), element by element (in place allowed): 0 the exact GELU, 1 the tanh GELU, 2 SiLU
+namespace celeg_b200 {
+// act() of the first `columns` columns of every row, in place; the rest of a row is left alone
+template <typename A>
+__global__ void activation_columns_kernel(A* x, long long stride, int columns, long long count, int kind) {
+    chain_release();
+    chain_wait();
+    const long long step = (long long)gridDim.x * blockDim.x;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < count; i += step) {
+        A* cell = x + (i / columns) * stride + (i % columns);
+        *cell = from_float<A>(activate(to_float(*cell), kind));
+    }
+}
+}  // namespace celeg_b200
+
+CELEG_API int celeg_activation_columns(void* x, long long stride, int columns, int rows, int kind, int act_dtype,
+                                       cudaStream_t stream) {
+    CELEG_REQUIRE(rows >= 0 && columns > 0 && stride >= columns && kind >= 0 && kind <= 4,
+                  "activation_columns: invalid sizes rows=%d columns=%d kind=%d", rows, columns, kind);
+    if (rows == 0) return 0;
+    const long long count = (long long)rows * columns;
+    const long long wanted = (count + 255) / 256;
+    const unsigned blocks = (unsigned)(wanted < 148LL * 16 ? wanted : 148LL * 16);
+    if (act_dtype == kFloat32)
+        launch_chained(activation_columns_kernel<float>, blocks, 256, 0, stream, (float*)x, stride, columns, count, kind);
+    else if (act_dtype == kBFloat16)
+        launch_chained(activation_columns_kernel<__nv_bfloat16>, blocks, 256, 0, stream, (__nv_bfloat16*)x, stride, columns,
+                       count, kind);
+    else
+        CELEG_REQUIRE(false, "activation_columns: unknown dtype code %d", act_dtype);
+    return check_launch("activation_columns");
+}
+
 CELEG_API int celeg_activation(const void* in, void* out, long long count, int kind, int act_dtype,
                                cudaStream_t stream) {
-    CELEG_REQUIRE(count >= 0 && kind >= 0 && kind <= 3, "activation: invalid count %lld or kind %d", count, kind);
+    CELEG_REQUIRE(count >= 0 && kind >= 0 && kind <= 4, "activation: invalid count %lld or kind %d", count, kind);
     if (count == 0) return 0;
     const int per_vector = act_dtype == kFloat32 ? 4 : 8;
     if ((act_dtype == kFloat32 || act_dtype == kBFloat16) && count % per_vector == 0 &&
@@ -183,4 +215,39 @@ CELEG_API int celeg_softcap(float* logits, long long count, float cap, cudaStrea
     if (count == 0) return 0;
     softcap_kernel<<<(unsigned)((count + 255) / 256), 256, 0, stream>>>(logits, count, cap, 1.0f / cap);
     return check_launch("softcap");
+}
+
+namespace celeg_b200 {
+// out = scale_a (a + bias_a) + scale_b b: the results of two mixers of the same input, side by side, as one output
+// owed to the stream. a, b float32 [rows, width] (b null: no second term); bias_a [width] or null; float32
+// arithmetic, rounded once.
+template <typename A>
+__global__ void scaled_sum_kernel(const float* a, const float* b, const float* bias_a, float scale_a, float scale_b,
+                                  A* out, long long count, int width) {
+    chain_release();
+    chain_wait();
+    const long long step = (long long)gridDim.x * blockDim.x;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < count; i += step) {
+        const float left = a[i] + (bias_a ? bias_a[i % width] : 0.0f);
+        out[i] = from_float<A>(b ? fmaf(scale_a, left, scale_b * b[i]) : scale_a * left);
+    }
+}
+}  // namespace celeg_b200
+
+CELEG_API int celeg_scaled_sum(const float* a, const float* b, const float* bias_a, float scale_a, float scale_b,
+                               void* out, int rows, int width, int act_dtype, cudaStream_t stream) {
+    CELEG_REQUIRE(rows >= 0 && width > 0, "scaled_sum: invalid sizes rows=%d width=%d", rows, width);
+    if (rows == 0) return 0;
+    const long long count = (long long)rows * width;
+    const long long wanted = (count + 255) / 256;
+    const unsigned blocks = (unsigned)(wanted < 148LL * 16 ? wanted : 148LL * 16);
+    if (act_dtype == kFloat32)
+        launch_chained(scaled_sum_kernel<float>, blocks, 256, 0, stream, a, b, bias_a, scale_a, scale_b, (float*)out, count,
+                       width);
+    else if (act_dtype == kBFloat16)
+        launch_chained(scaled_sum_kernel<__nv_bfloat16>, blocks, 256, 0, stream, a, b, bias_a, scale_a, scale_b,
+                       (__nv_bfloat16*)out, count, width);
+    else
+        CELEG_REQUIRE(false, "scaled_sum: unknown dtype code %d", act_dtype);
+    return check_launch("scaled_sum");
 }

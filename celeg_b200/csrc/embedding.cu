@@ -1,5 +1,7 @@
 // Embedding gather: residual[t, :] = multiplier * table[token[t], :], written as float32
-// (the residual stream is kept in 32-bit on both precision paths).
+// (the residual stream is kept in 32-bit on both precision paths). With positions and a table of frequencies a
+// sinusoidal vector of the token's position is added: entry 2i gets sin(p f_i), entry 2i + 1 cos(p f_i), the
+// angle a float32 product, sine and cosine the precise float32 functions.
 // Counterpart in celeg: embedding_batch_kernel (src/backend/cuda/kernels/embedding.cu:26).
 #include "common.cuh"
 
@@ -8,7 +10,8 @@ namespace celeg_b200 {
 // next_w != null: the first half of a split RMSNorm (gemv_bf16.cu) for the norm that follows:
 // xw_out[t, :] = bf16(residual * next_w) and sumsq_out[t] = sum(residual^2).
 template <typename W>
-__global__ void embedding_kernel(const W* __restrict__ table, const int* tokens,
+__global__ void embedding_kernel(const W* __restrict__ table, const int* tokens, const int* positions,
+                                 const float* __restrict__ frequencies,
                                  float* out, int hidden, int vocab, float multiplier, const float* next_w,
                                  __nv_bfloat16* xw_out, float* sumsq_out, int sumsq_stride) {
     __shared__ float scratch[33];
@@ -20,8 +23,13 @@ __global__ void embedding_kernel(const W* __restrict__ table, const int* tokens,
     const bool valid = token >= 0 && token < vocab;          // the host refuses other ids before launch
     const W* src = table + (size_t)(valid ? token : 0) * hidden;
     float squares = 0.0f;
+    const float place = frequencies ? (float)positions[row] : 0.0f;
     for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
-        const float v = valid ? to_float(src[i]) * multiplier : 0.0f;
+        float v = valid ? to_float(src[i]) * multiplier : 0.0f;
+        if (frequencies) {
+            const float angle = place * frequencies[i >> 1];
+            v += (i & 1) ? cosf(angle) : sinf(angle);
+        }
         dst[i] = v;
         if (next_w) {
             xw_out[(size_t)row * hidden + i] = __float2bfloat16_rn(v * next_w[i]);
@@ -38,7 +46,8 @@ __global__ void embedding_kernel(const W* __restrict__ table, const int* tokens,
 
 using namespace celeg_b200;
 
-static int embedding_checked(const void* table, int table_dtype, const int* tokens, float* out, int rows, int hidden,
+static int embedding_checked(const void* table, int table_dtype, const int* tokens, const int* positions,
+                             const float* frequencies, float* out, int rows, int hidden,
                              int vocab, float multiplier, const float* next_w, void* xw_out, float* sumsq_out,
                              int sumsq_stride, cudaStream_t stream) {
     CELEG_REQUIRE(rows >= 0 && hidden > 0 && vocab > 0, "embedding: invalid sizes rows=%d hidden=%d vocab=%d",
@@ -48,11 +57,11 @@ static int embedding_checked(const void* table, int table_dtype, const int* toke
     if (rows == 0) return 0;
     const int threads = hidden >= 1024 ? 256 : 128;
     if (table_dtype == kFloat32)
-        launch_chained(embedding_kernel<float>, rows, threads, 0, stream, (const float*)table, tokens, out, hidden,
-                       vocab, multiplier, next_w, (__nv_bfloat16*)xw_out, sumsq_out, sumsq_stride);
+        launch_chained(embedding_kernel<float>, rows, threads, 0, stream, (const float*)table, tokens, positions,
+                       frequencies, out, hidden, vocab, multiplier, next_w, (__nv_bfloat16*)xw_out, sumsq_out, sumsq_stride);
     else if (table_dtype == kBFloat16)
         launch_chained(embedding_kernel<__nv_bfloat16>, rows, threads, 0, stream, (const __nv_bfloat16*)table,
-                       tokens, out, hidden, vocab, multiplier, next_w, (__nv_bfloat16*)xw_out, sumsq_out, sumsq_stride);
+                       tokens, positions, frequencies, out, hidden, vocab, multiplier, next_w, (__nv_bfloat16*)xw_out, sumsq_out, sumsq_stride);
     else
         CELEG_REQUIRE(false, "embedding: unknown dtype code %d", table_dtype);
     return check_launch("embedding");
@@ -60,8 +69,8 @@ static int embedding_checked(const void* table, int table_dtype, const int* toke
 
 CELEG_API int celeg_embedding(const void* table, int table_dtype, const int* tokens, float* out, int rows,
                               int hidden, int vocab, float multiplier, cudaStream_t stream) {
-    return embedding_checked(table, table_dtype, tokens, out, rows, hidden, vocab, multiplier, nullptr, nullptr,
-                             nullptr, 0, stream);
+    return embedding_checked(table, table_dtype, tokens, nullptr, nullptr, out, rows, hidden, vocab, multiplier, nullptr,
+                             nullptr, nullptr, 0, stream);
 }
 
 // The gather and, for the RMSNorm that follows, the first half of a split norm: xw_out [rows, hidden]
@@ -69,6 +78,17 @@ CELEG_API int celeg_embedding(const void* table, int table_dtype, const int* tok
 CELEG_API int celeg_embedding_split_norm(const void* table, int table_dtype, const int* tokens, float* out, int rows,
                                          int hidden, int vocab, float multiplier, const float* next_w, void* xw_out,
                                          float* sumsq_out, int sumsq_stride, cudaStream_t stream) {
-    return embedding_checked(table, table_dtype, tokens, out, rows, hidden, vocab, multiplier, next_w, xw_out,
-                             sumsq_out, sumsq_stride, stream);
+    return embedding_checked(table, table_dtype, tokens, nullptr, nullptr, out, rows, hidden, vocab, multiplier, next_w,
+                             xw_out, sumsq_out, sumsq_stride, stream);
+}
+
+// The gather plus the sinusoidal vector of each token's position (frequencies: float32 [(hidden + 1) / 2]); next_w
+// may be null (no norm prepared).
+CELEG_API int celeg_embedding_sinusoid(const void* table, int table_dtype, const int* tokens, const int* positions,
+                                       const float* frequencies, float* out, int rows, int hidden, int vocab,
+                                       float multiplier, const float* next_w, void* xw_out, float* sumsq_out,
+                                       int sumsq_stride, cudaStream_t stream) {
+    CELEG_REQUIRE(positions && frequencies, "embedding: a position vector needs positions and frequencies");
+    return embedding_checked(table, table_dtype, tokens, positions, frequencies, out, rows, hidden, vocab, multiplier,
+                             next_w, xw_out, sumsq_out, sumsq_stride, stream);
 }

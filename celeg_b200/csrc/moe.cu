@@ -32,7 +32,7 @@ __device__ __forceinline__ float expert_activation(float z, int kind) {
 // ------------------------------------------------------------------------------------------------ router
 // logits: float32 [tokens, stride] = h W_r^T from a product with float32 sums (column `experts`, if asked for, is the
 // shared expert's gate before its sigmoid). One warp a token: softmax over all experts, the choice, the weights.
-__global__ void moe_route_kernel(const float* logits, int stride, const float* correction, int gate_column,
+__global__ void moe_route_kernel(const float* logits, int stride, const float* bias, const float* correction, int gate_column,
                                  int* chosen, float* weights, float* shared_gate, int tokens, int experts, int top) {
     extern __shared__ float route_smem[];          // per warp: scores [experts]
     chain_release();
@@ -44,11 +44,12 @@ __global__ void moe_route_kernel(const float* logits, int stride, const float* c
     const float* row = logits + (size_t)t * stride;
     if (gate_column >= 0 && lane == 0) shared_gate[t] = 1.0f / (1.0f + expf(-row[gate_column]));
     float largest = -INFINITY;
-    for (int e = lane; e < experts; e += 32) largest = fmaxf(largest, row[e]);
+    // (a bias of the logits shifts choice and weights alike)
+    for (int e = lane; e < experts; e += 32) largest = fmaxf(largest, row[e] + (bias ? bias[e] : 0.0f));
     largest = warp_max(largest);
     float total = 0.0f;
     for (int e = lane; e < experts; e += 32) {
-        const float p = expf(row[e] - largest);
+        const float p = expf(row[e] + (bias ? bias[e] : 0.0f) - largest);
         scores[e] = p;
         total += p;
     }
@@ -378,7 +379,7 @@ __global__ void moe_combine_vec_kernel(const __nv_bfloat16* expert_out, int out_
 
 using namespace celeg_b200;
 
-CELEG_API int celeg_moe_route(const float* logits, int stride, const float* correction, int gate_column, int* chosen,
+CELEG_API int celeg_moe_route(const float* logits, int stride, const float* bias, const float* correction, int gate_column, int* chosen,
                               float* weights, float* shared_gate, int tokens, int experts, int top, cudaStream_t stream) {
     CELEG_REQUIRE(tokens >= 0 && experts > 0 && top > 0 && top <= experts && stride >= experts,
                   "moe_route: invalid sizes tokens=%d experts=%d top=%d stride=%d", tokens, experts, top, stride);
@@ -389,7 +390,7 @@ CELEG_API int celeg_moe_route(const float* logits, int stride, const float* corr
     const int warps = 4;
     const size_t smem = (size_t)warps * experts * sizeof(float);
     const unsigned blocks = (unsigned)((tokens + warps - 1) / warps);
-    launch_chained(moe_route_kernel, blocks, warps * 32, smem, stream, logits, stride, correction, gate_column, chosen,
+    launch_chained(moe_route_kernel, blocks, warps * 32, smem, stream, logits, stride, bias, correction, gate_column, chosen,
                    weights, shared_gate, tokens, experts, top);
     return check_launch("moe_route");
 }

@@ -411,6 +411,9 @@ struct DecodeStepParams {
     int heads, kv_heads, dim, vdim;
     float q_scale;
     void* out;                                     // [tokens, heads * vdim], activation type
+    int input_act;                                 // retention, mLSTM: an activation of q, k and v as read (-1: none)
+    float* raw_out;                                // not null: the read-outs go here as they are, float32 [tokens,
+                                                   // heads * vdim], and norm and gate are the caller's (one over all heads)
 };
 
 template <int MODE, typename A>
@@ -448,6 +451,10 @@ __global__ void __launch_bounds__(256) recurrent_decode_kernel(const DecodeStepP
         } else {
             kv = row[p.k_off + qk_head * dim + e];
             qv = row[p.q_off + qk_head * dim + e];
+            if (p.input_act >= 0) {
+                kv = activate(kv, p.input_act);
+                qv = activate(qv, p.input_act);
+            }
         }
         k_s[e] = kv;
         q_s[e] = qv;
@@ -546,7 +553,8 @@ __global__ void __launch_bounds__(256) recurrent_decode_kernel(const DecodeStepP
                 sq += part_s[(warps + w) * 32 + lane];
             }
             if (MODE != kScanRetention) sq *= p.q_scale;
-            const float vj = MODE == kScanDelta ? convolved(p.v_off + head * vdim + j) : row[p.v_off + head * vdim + j];
+            float vj = MODE == kScanDelta ? convolved(p.v_off + head * vdim + j) : row[p.v_off + head * vdim + j];
+            if (MODE != kScanDelta && p.input_act >= 0) vj = activate(vj, p.input_act);
             float o, scale, add;
             if (MODE == kScanRetention) {
                 add = vj * p.q_scale;                 // the key's factor: S holds scaled keys
@@ -583,6 +591,12 @@ __global__ void __launch_bounds__(256) recurrent_decode_kernel(const DecodeStepP
         __syncthreads();                              // every thread has read n and m
         for (int e = threadIdx.x; e < dim; e += blockDim.x) n_head[e] = fmaf(k_s[e], write, keep * n_head[e]);
         if (threadIdx.x == 0) *m_head = m_new;
+    }
+    if (p.raw_out) {
+        __syncthreads();
+        float* raw = p.raw_out + ((size_t)t * heads + head) * vdim;
+        for (int j = threadIdx.x; j < vdim; j += blockDim.x) raw[j] = o_s[j];
+        return;
     }
     squares = block_sum(squares, scratch);
     const float inv = 1.0f / sqrtf(squares / (float)vdim + p.eps);
@@ -928,13 +942,13 @@ CELEG_API int celeg_gated_head_norm(const float* o, const float* gate, int gate_
 // the first ``channels`` columns of a row, bias0 = A_log, bias1 = dt_bias, the output gate is SiLU; the carried
 // inputs are moved on by a second launch. mode 1 (mLSTM): bias0 / bias1 = the gates' biases, the gate is a sigmoid.
 // mode 2 (retention): bias0 = the heads' decays, the output gate is SiLU, norm_w may be null (no weight).
-CELEG_API int celeg_recurrent_decode(int mode, const float* proj, int stride, int q_off, int k_off, int v_off,
-                                     int gate_off, int g0_off, int g1_off, const float* conv_kernel, float* carried,
-                                     int taps, int channels, const float* bias0, const float* bias1, float cap,
-                                     const float* norm_w, int norm_per_head, float eps, float unit_eps, float* state,
-                                     long long slot_stride, const int* span_begin, const int* span_slot, int tokens,
-                                     int heads, int kv_heads, int dim, int vdim, float q_scale, void* out,
-                                     int act_dtype, cudaStream_t stream) {
+static int recurrent_decode_launch(int mode, const float* proj, int stride, int q_off, int k_off, int v_off,
+                                   int gate_off, int g0_off, int g1_off, const float* conv_kernel, float* carried,
+                                   int taps, int channels, const float* bias0, const float* bias1, float cap,
+                                   const float* norm_w, int norm_per_head, float eps, float unit_eps, float* state,
+                                   long long slot_stride, const int* span_begin, const int* span_slot, int tokens,
+                                   int heads, int kv_heads, int dim, int vdim, float q_scale, void* out,
+                                   int act_dtype, int input_act, float* raw_out, cudaStream_t stream) {
     CELEG_REQUIRE(tokens >= 0 && heads > 0 && kv_heads > 0 && heads % kv_heads == 0 && dim > 0 && vdim > 0,
                   "recurrent_decode: invalid sizes tokens=%d heads=%d kv_heads=%d dim=%d vdim=%d", tokens, heads,
                   kv_heads, dim, vdim);
@@ -949,7 +963,7 @@ CELEG_API int celeg_recurrent_decode(int mode, const float* proj, int stride, in
     if (tokens == 0) return 0;
     const DecodeStepParams p = {proj, stride, q_off, k_off, v_off, gate_off, g0_off, g1_off, conv_kernel, carried, taps,
                                 channels, bias0, bias1, cap, norm_w, norm_per_head, eps, unit_eps, state, slot_stride,
-                                span_slot, heads, kv_heads, dim, vdim, q_scale, out};
+                                span_slot, heads, kv_heads, dim, vdim, q_scale, out, input_act, raw_out};
     dim3 grid(heads, tokens);
     if (mode == kScanDelta) {
         if (act_dtype == kFloat32)
@@ -975,6 +989,33 @@ CELEG_API int celeg_recurrent_decode(int mode, const float* proj, int stride, in
     else
         launch_chained(recurrent_decode_kernel<kScanMlstm, __nv_bfloat16>, grid, kDecodeStepThreads, smem, stream, p);
     return check_launch("recurrent_decode");
+}
+
+CELEG_API int celeg_recurrent_decode(int mode, const float* proj, int stride, int q_off, int k_off, int v_off,
+                                     int gate_off, int g0_off, int g1_off, const float* conv_kernel, float* carried,
+                                     int taps, int channels, const float* bias0, const float* bias1, float cap,
+                                     const float* norm_w, int norm_per_head, float eps, float unit_eps, float* state,
+                                     long long slot_stride, const int* span_begin, const int* span_slot, int tokens,
+                                     int heads, int kv_heads, int dim, int vdim, float q_scale, void* out,
+                                     int act_dtype, cudaStream_t stream) {
+    return recurrent_decode_launch(mode, proj, stride, q_off, k_off, v_off, gate_off, g0_off, g1_off, conv_kernel, carried,
+                                   taps, channels, bias0, bias1, cap, norm_w, norm_per_head, eps, unit_eps, state,
+                                   slot_stride, span_begin, span_slot, tokens, heads, kv_heads, dim, vdim, q_scale, out,
+                                   act_dtype, -1, nullptr, stream);
+}
+
+// The retention's decoding step with an activation of q, k and v as they are read (input_act: a code of activate(), or
+// -1) and the read-outs left as they are in raw_out (float32 [tokens, heads * vdim]): for a mixer whose norm runs over
+// all heads together, which no block of this launch sees.
+CELEG_API int celeg_retention_decode_raw(const float* proj, int stride, int q_off, int k_off, int v_off,
+                                         const float* decay, float* state, long long slot_stride, const int* span_slot,
+                                         int tokens, int heads, int dim, int vdim, float q_scale, int input_act,
+                                         float* raw_out, cudaStream_t stream) {
+    CELEG_REQUIRE(raw_out != nullptr && input_act >= -1 && input_act <= 3, "retention_decode_raw: no output or activation %d",
+                  input_act);
+    return recurrent_decode_launch(kScanRetention, proj, stride, q_off, k_off, v_off, 0, 0, 0, nullptr, nullptr, 0, 0, decay,
+                                   decay, 0.0f, nullptr, 0, 1.0f, 0.0f, state, slot_stride, nullptr, span_slot, tokens,
+                                   heads, heads, dim, vdim, q_scale, raw_out, kFloat32, input_act, raw_out, stream);
 }
 
 // Retention over the step's spans in segments of `segment` tokens (a multiple of 64). Scratch: floats

@@ -36,7 +36,8 @@ def build_part(category: str, part: Optional[PartSpec], tensors: Mapping[str, to
 
 class Layer:
     """The parts of one block, built: the four named ones and whatever else the description lists, all under
-    their names in ``parts`` (what the arrangement gets). ``cache_parts`` are those that ask for a cache."""
+    their names in ``parts`` (what the arrangement gets). ``cache_parts`` are those that ask for a cache, the
+    parts nested in a part that holds several included."""
 
     def __init__(self, spec: LayerSpec, tensors: Mapping[str, torch.Tensor], rt: Runtime):
         self.name = spec.name
@@ -53,9 +54,21 @@ class Layer:
                 raise ValueError(f"layer {spec.name}: the extra part '{name}' does not state its category")
             self.parts[name] = build_part(part.category, part, tensors, rt)
         self.mixer = self.parts["mixer"]
-        self.cache_parts = {name: part for name, part in self.parts.items()
-                            if part is not None and hasattr(part, "cache_need")}
+        self.cache_parts: Dict[str, object] = {}
+        for name, part in self.parts.items():
+            self._collect_cache_parts(name, part)
         self.block = part_factory("arrangement", spec.arrangement)(self.parts, rt)
+
+
+    def _collect_cache_parts(self, name: str, part) -> None:
+        """A part that asks for a cache is a cache part under its name; a part that holds others (``children``: a
+        mixer made of two mixers side by side) passes theirs on as ``<its name>.<child's name>``."""
+        if part is None:
+            return
+        if hasattr(part, "cache_need"):
+            self.cache_parts[name] = part
+        for child_name, child in (getattr(part, "children", None) or {}).items():
+            self._collect_cache_parts(f"{name}.{child_name}", child)
 
 
 class Model:

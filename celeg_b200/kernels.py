@@ -44,9 +44,26 @@ _SIGNATURES = {
     "celeg_qk_norm_rope_store": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
                                  c_void_p, c_void_p, c_longlong, c_int, c_int, c_int, c_int, c_int, c_int, c_float,
                                  c_int, c_void_p, c_int, c_void_p],
-    "celeg_attention_generic": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_longlong, c_void_p, c_void_p,
-                                c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p, c_void_p,
-                                c_int, c_void_p],
+    "celeg_attention_generic": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_longlong, c_longlong, c_int, c_int,
+                                c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float,
+                                c_void_p, c_void_p, c_int, c_void_p],
+    "celeg_bias_store_kv": [c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
+                            c_void_p, c_longlong, c_longlong, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
+                            c_void_p, c_int, c_void_p],
+    "celeg_embedding_sinusoid": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_float,
+                                 c_void_p, c_void_p, c_void_p, c_int, c_void_p],
+    "celeg_lru_prepare": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_longlong, c_void_p, c_void_p, c_void_p,
+                          c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
+    "celeg_block_diagonal_product": [c_void_p, c_int, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p],
+    "celeg_lru_scan": [c_void_p, c_void_p, c_void_p, c_void_p, c_float, c_void_p, c_void_p, c_void_p, c_longlong, c_void_p,
+                       c_void_p, c_int, c_int, c_int, c_int, c_void_p],
+    "celeg_lru_decode": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_longlong, c_void_p, c_void_p,
+                         c_void_p, c_void_p, c_float, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p],
+    "celeg_retention_decode_raw": [c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_longlong, c_void_p, c_int,
+                                   c_int, c_int, c_int, c_float, c_int, c_void_p, c_void_p],
+    "celeg_activation_columns": [c_void_p, c_longlong, c_int, c_int, c_int, c_int, c_void_p],
+    "celeg_glu": [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
+    "celeg_scaled_sum": [c_void_p, c_void_p, c_void_p, c_float, c_float, c_void_p, c_int, c_int, c_int, c_void_p],
     "celeg_attention_decode": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_longlong, c_void_p, c_void_p,
                                c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int,
                                c_void_p, c_void_p, c_void_p, c_void_p, c_void_p],
@@ -114,7 +131,7 @@ _SIGNATURES = {
     "celeg_head_project": [c_void_p, c_int, c_int, c_void_p, c_longlong, c_longlong, c_longlong, c_void_p, c_int, c_int,
                            c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
     "celeg_head_gate": [c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
-    "celeg_moe_route": [c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
+    "celeg_moe_route": [c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
     "celeg_moe_group": [c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p],
     "celeg_moe_gather_rows": [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
     "celeg_gemm_tcgen05_grouped": [c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_void_p, c_int, c_void_p, c_int, c_int,
@@ -190,14 +207,30 @@ class SplitNorm:
 
 
 def embedding(table: torch.Tensor, tokens: torch.Tensor, out: torch.Tensor, multiplier: float = 1.0,
-              prepare: Optional[SplitNorm] = None, next_weight: Optional[torch.Tensor] = None) -> None:
+              prepare: Optional[SplitNorm] = None, next_weight: Optional[torch.Tensor] = None,
+              positions: Optional[torch.Tensor] = None, frequencies: Optional[torch.Tensor] = None) -> None:
     """out[t] = multiplier * table[tokens[t]]. With ``prepare``: also the first half of the norm whose
-    weight is ``next_weight`` (``prepare.xw`` and one sum of squares per row are written)."""
+    weight is ``next_weight`` (``prepare.xw`` and one sum of squares per row are written). With ``positions`` and
+    ``frequencies`` (float32 [(hidden + 1) // 2]): plus a sinusoidal vector of the position, entry 2i
+    sin(p f_i), entry 2i + 1 cos(p f_i)."""
     rows = tokens.shape[0]
     _need(tokens, torch.int32, "tokens")
     _need(out, torch.float32, "out")
     vocab, hidden = table.shape
     assert out.shape[0] >= rows and out.shape[1] == hidden
+    if frequencies is not None:
+        _need(frequencies, torch.float32, "frequencies")
+        _need(positions, torch.int32, "positions")
+        assert frequencies.numel() >= (hidden + 1) // 2 and positions.numel() >= rows
+        if prepare is not None:
+            _need(next_weight, torch.float32, "next_weight")
+            assert prepare.xw.dtype == torch.bfloat16 and prepare.xw.stride(0) == hidden and prepare.partials == 1
+        _check(library().celeg_embedding_sinusoid(
+            _ptr(table), dtype_code(table.dtype), _ptr(tokens), _ptr(positions), _ptr(frequencies), _ptr(out), rows,
+            hidden, vocab, multiplier, _ptr(next_weight) if prepare is not None else None,
+            _ptr(prepare.xw) if prepare is not None else None, _ptr(prepare.sumsq) if prepare is not None else None,
+            prepare.sumsq.stride(0) if prepare is not None else 0, _stream()))
+        return
     if prepare is None:
         _check(library().celeg_embedding(_ptr(table), dtype_code(table.dtype), _ptr(tokens), _ptr(out), rows, hidden,
                                          vocab, multiplier, _stream()))
@@ -284,15 +317,39 @@ def attention_generic(q: torch.Tensor, q_row_stride: int, out: torch.Tensor, k_c
                       v_cache: torch.Tensor, positions: torch.Tensor, token_span: torch.Tensor,
                       block_table: torch.Tensor, tokens: int, q_heads: int, kv_heads: int, head_dim: int,
                       page_tokens: int, window: Optional[int], scale: float, error_flag: torch.Tensor,
-                      sinks: Optional[torch.Tensor] = None) -> None:
+                      sinks: Optional[torch.Tensor] = None, value_dim: Optional[int] = None,
+                      chunk: Optional[int] = None) -> None:
     """``sinks``: float32 [q_heads] or None; a head's sink is a score that enters the denominator of each of its
-    rows once, unscaled, without key or value."""
+    rows once, unscaled, without key or value. ``value_dim``: the values' size when it is not the keys' (``out`` is
+    then [tokens, q_heads * value_dim]). ``chunk``: a query reads only the keys of its own chunk of that many
+    positions, counted from position 0 (no window then)."""
     if sinks is not None:
         _need(sinks, torch.float32, "sinks")
     _check(library().celeg_attention_generic(
-        _ptr(q), q_row_stride, _ptr(out), _ptr(k_cache), _ptr(v_cache), k_cache.stride(0), _ptr(positions),
+        _ptr(q), q_row_stride, _ptr(out), _ptr(k_cache), _ptr(v_cache), k_cache.stride(0), v_cache.stride(0),
+        int(value_dim or 0), int(chunk or 0), _ptr(positions),
         _ptr(token_span), _ptr(block_table), block_table.stride(0), tokens, q_heads, kv_heads, head_dim,
         page_tokens, int(window or 0), scale, _ptr(sinks), _ptr(error_flag), dtype_code(q.dtype), _stream()))
+
+
+def bias_store_kv(proj: torch.Tensor, bias: Optional[torch.Tensor], q_out: torch.Tensor, positions: torch.Tensor,
+                  token_span: torch.Tensor, block_table: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
+                  tokens: int, q_heads: int, kv_heads: int, head_dim: int, value_dim: int, key_store: int,
+                  value_store: int, page_tokens: int, error_flag: torch.Tensor) -> None:
+    """Float32 rows [q heads | k heads | v heads] as projected (values ``value_dim`` wide): ``bias`` (float32, a row's
+    width, or None) is added and the sums are rounded once, q into ``q_out`` and k and v into the tokens' places in
+    the paged cache. ``key_store`` / ``value_store``: the sizes of a stored head (queries and keys / values); what a
+    stored head has beyond the projected one is written as zeros."""
+    _need(proj, torch.float32, "proj")
+    if bias is not None:
+        _need(bias, torch.float32, "bias")
+        assert bias.numel() == q_heads * head_dim + kv_heads * (head_dim + value_dim)
+    assert q_out.dtype == k_cache.dtype == v_cache.dtype and q_out.stride(-1) == 1 and proj.stride(-1) == 1
+    _check(library().celeg_bias_store_kv(
+        _ptr(proj), proj.stride(0), _ptr(bias), _ptr(q_out), q_out.stride(0), _ptr(positions), _ptr(token_span),
+        _ptr(block_table), block_table.stride(0), _ptr(k_cache), _ptr(v_cache), k_cache.stride(0), v_cache.stride(0),
+        tokens, q_heads, kv_heads, head_dim, value_dim, key_store, value_store, page_tokens, _ptr(error_flag),
+        dtype_code(q_out.dtype), _stream()))
 
 
 def attention_decode_supported(q_heads: int, kv_heads: int, head_dim: int, dtype: torch.dtype) -> bool:
@@ -393,7 +450,7 @@ def attention_prefill_tcgen05(q: torch.Tensor, q_row_stride: int, out: torch.Ten
         head_dim, page_tokens, int(window or 0), scale, _ptr(sinks), _ptr(error_flag), _stream()))
 
 
-ACT_GELU_ERF, ACT_GELU_TANH, ACT_SILU, ACT_RELU_SQUARED = 0, 1, 2, 3      # codes of csrc/common.cuh: activate()
+ACT_GELU_ERF, ACT_GELU_TANH, ACT_SILU, ACT_RELU_SQUARED, ACT_RELU = 0, 1, 2, 3, 4      # codes of csrc/common.cuh: activate()
 GEMV_MAX_ROWS = 16
 GEMV_STORE, GEMV_STORE_F32, GEMV_ADD_RESIDUAL, GEMV_SWIGLU, GEMV_CONV, GEMV_ACTIVATION = 0, 1, 2, 3, 4, 5
 
@@ -480,6 +537,11 @@ def gemm_tcgen05(x: torch.Tensor, w: torch.Tensor, y: torch.Tensor, rows: int, e
 
 def swiglu(gate_up: torch.Tensor, out: torch.Tensor, tokens: int, inner: int) -> None:
     _check(library().celeg_swiglu(_ptr(gate_up), _ptr(out), tokens, inner, dtype_code(gate_up.dtype), _stream()))
+
+
+def glu(gate_up: torch.Tensor, out: torch.Tensor, tokens: int, inner: int, kind: int) -> None:
+    """out[:tokens] = act(gate) * up of rows [gate | up] (``inner`` each), ``kind`` one of ACT_*."""
+    _check(library().celeg_glu(_ptr(gate_up), _ptr(out), tokens, inner, kind, dtype_code(gate_up.dtype), _stream()))
 
 
 def gemm_f32(x: torch.Tensor, w: torch.Tensor, y: torch.Tensor, m: int, accumulate: bool = False) -> None:
@@ -582,6 +644,25 @@ def activation(x: torch.Tensor, out: torch.Tensor, rows: int, kind: int) -> None
     """out[:rows] = act(x[:rows]) element by element (in place allowed); both contiguous, same shape."""
     assert x.is_contiguous() and out.is_contiguous() and x.shape[1:] == out.shape[1:] and x.dtype == out.dtype
     _check(library().celeg_activation(_ptr(x), _ptr(out), rows * x.shape[1], kind, dtype_code(x.dtype), _stream()))
+
+
+def activation_columns(x: torch.Tensor, columns: int, rows: int, kind: int) -> None:
+    """act() of the first ``columns`` columns of x[:rows], in place; the other columns are left alone."""
+    assert x.stride(-1) == 1 and columns <= x.shape[1]
+    _check(library().celeg_activation_columns(_ptr(x), x.stride(0), columns, rows, kind, dtype_code(x.dtype), _stream()))
+
+
+def scaled_sum(a: torch.Tensor, b: Optional[torch.Tensor], bias_a: Optional[torch.Tensor], scale_a: float, scale_b: float,
+               out: torch.Tensor, rows: int) -> None:
+    """out[:rows] = scale_a (a + bias_a) + scale_b b; a, b float32 [rows, width] (b None: no second term), float32
+    arithmetic, rounded once."""
+    _need(a, torch.float32, "a")
+    assert a.is_contiguous() and a.shape[1] == out.shape[1] and out.is_contiguous()
+    if b is not None:
+        _need(b, torch.float32, "b")
+        assert b.is_contiguous() and b.shape[1] == a.shape[1]
+    _check(library().celeg_scaled_sum(_ptr(a), _ptr(b), _ptr(bias_a), scale_a, scale_b, _ptr(out), rows, a.shape[1],
+                                      dtype_code(out.dtype), _stream()))
 
 
 def softcap(logits: torch.Tensor, rows: int, cap: float) -> None:
@@ -689,6 +770,75 @@ def gated_head_norm(o: torch.Tensor, gate: torch.Tensor, weight: Optional[torch.
                                            _stream()))
 
 
+def retention_decode_raw(proj: torch.Tensor, offsets: Tuple[int, int, int], decay: torch.Tensor, state: torch.Tensor,
+                         slot_stride: int, span_slot: torch.Tensor, tokens: int, heads: int, dim: int, vdim: int,
+                         q_scale: float, input_act: int, raw_out: torch.Tensor) -> None:
+    """A decoding step of the retention (S <- d S + k v^T, read-out S^T q) that leaves the read-outs as they are in
+    ``raw_out`` (float32 [tokens, heads * vdim]); ``input_act``: an activation of q, k and v as they are read out of
+    ``proj`` (a code of ACT_*, or -1). ``offsets``: columns of (q, k, v) in a row of ``proj`` (float32)."""
+    assert proj.dtype == torch.float32 and proj.stride(-1) == 1 and raw_out.dtype == torch.float32
+    assert raw_out.is_contiguous() and raw_out.shape[1] == heads * vdim and decay.shape == (heads,)
+    _check(library().celeg_retention_decode_raw(_ptr(proj), proj.stride(0), *offsets, _ptr(decay), _ptr(state),
+                                                slot_stride, _ptr(span_slot), tokens, heads, dim, vdim, q_scale,
+                                                input_act, _ptr(raw_out), _stream()))
+
+
+# ------------------------------------------------------------- gated linear recurrent unit over channels
+def lru_prepare(proj: torch.Tensor, bias: Optional[torch.Tensor], taps: torch.Tensor, conv_bias: Optional[torch.Tensor],
+                carried: torch.Tensor, slot_stride: int, token_span: torch.Tensor, span_begin: torch.Tensor,
+                span_slot: torch.Tensor, y_out: torch.Tensor, u_out: torch.Tensor, tokens: int, spans: int, width: int,
+                n_taps: int) -> None:
+    """Rows [y | x] of ``proj`` (float32): y_out = gelu_tanh(y + b_y), u_out = conv(x + b_x) + b_c over each span with
+    the carried inputs before its start; then the carried inputs are moved on (a second launch)."""
+    for tensor in (proj, taps, carried, y_out, u_out):
+        assert tensor.dtype == torch.float32 and tensor.stride(-1) == 1
+    assert y_out.is_contiguous() and u_out.is_contiguous() and y_out.shape[1] == width and u_out.shape[1] == width
+    _check(library().celeg_lru_prepare(_ptr(proj), proj.stride(0), _ptr(bias), _ptr(taps), _ptr(conv_bias), _ptr(carried),
+                                       slot_stride, _ptr(token_span), _ptr(span_begin), _ptr(span_slot), _ptr(y_out),
+                                       _ptr(u_out), tokens, spans, width, n_taps, _stream()))
+    global LAUNCHES
+    LAUNCHES += 1 if n_taps > 1 else 0
+
+
+def block_diagonal_product(x: torch.Tensor, x_parts: int, w: torch.Tensor, y: torch.Tensor, rows: int) -> None:
+    """y[:rows, z n:(z + 1) n] = x[:rows, (z % x_parts) k:...] @ w[z]^T for every z; w float32 [batches, n, k]."""
+    batches, n, k = w.shape
+    for tensor in (x, w, y):
+        assert tensor.dtype == torch.float32 and tensor.stride(-1) == 1
+    assert w.is_contiguous()
+    _check(library().celeg_block_diagonal_product(_ptr(x), x.stride(0), x_parts, _ptr(w), _ptr(y), y.stride(0), rows, n,
+                                                  k, batches, _stream()))
+
+
+def lru_scan(gates: torch.Tensor, u: torch.Tensor, gate_bias: Optional[torch.Tensor], lam: torch.Tensor, c: float,
+             y: torch.Tensor, out: torch.Tensor, state: torch.Tensor, slot_stride: int, span_begin: torch.Tensor,
+             span_slot: torch.Tensor, tokens: int, spans: int, width: int) -> None:
+    """gates float32 [tokens, 2 * width] (the gates' sums; rewritten as decay | input), then S <- a S + b along every
+    span with S in the slots, out = S y in the activation type (two launches)."""
+    for tensor in (gates, u, lam, y, state):
+        assert tensor.dtype == torch.float32 and tensor.stride(-1) == 1
+    assert gates.is_contiguous() and gates.shape[1] == 2 * width and u.is_contiguous() and y.is_contiguous()
+    assert out.is_contiguous() and out.shape[1] == width
+    _check(library().celeg_lru_scan(_ptr(gates), _ptr(u), _ptr(gate_bias), _ptr(lam), c, _ptr(y), _ptr(out), _ptr(state),
+                                    slot_stride, _ptr(span_begin), _ptr(span_slot), tokens, spans, width,
+                                    dtype_code(out.dtype), _stream()))
+    global LAUNCHES
+    LAUNCHES += 1
+
+
+def lru_decode(proj: torch.Tensor, bias: Optional[torch.Tensor], taps: torch.Tensor, conv_bias: Optional[torch.Tensor],
+               carried: torch.Tensor, state: torch.Tensor, slot_stride: int, span_slot: torch.Tensor,
+               gate_w: torch.Tensor, gate_bias: Optional[torch.Tensor], lam: torch.Tensor, c: float, out: torch.Tensor,
+               tokens: int, width: int, n_taps: int, blocks: int) -> None:
+    """One token a request: the whole unit between its two projections in one launch (csrc/linear_recurrence.cu)."""
+    for tensor in (proj, taps, carried, state, gate_w, lam):
+        assert tensor.dtype == torch.float32 and tensor.stride(-1) == 1
+    assert gate_w.is_contiguous() and out.is_contiguous() and out.shape[1] == width
+    _check(library().celeg_lru_decode(_ptr(proj), proj.stride(0), _ptr(bias), _ptr(taps), _ptr(conv_bias), _ptr(carried),
+                                      _ptr(state), slot_stride, _ptr(span_slot), _ptr(gate_w), _ptr(gate_bias), _ptr(lam),
+                                      c, _ptr(out), tokens, width, n_taps, blocks, dtype_code(out.dtype), _stream()))
+
+
 # ------------------------------------------- depth average, latent attention, mixture of experts
 def depth_average(stream: torch.Tensor, delta_a: Optional[torch.Tensor], delta_b: Optional[torch.Tensor],
                   history: torch.Tensor, weights: torch.Tensor, index: int, n_rows: int,
@@ -761,14 +911,19 @@ def moe_max_tiles(pairs: int, experts: int, tile_rows: int = MOE_TILE) -> int:
 
 def moe_route(logits: torch.Tensor, experts: int, correction: Optional[torch.Tensor], gate_column: Optional[int],
               chosen: torch.Tensor, weights: torch.Tensor, shared_gate: Optional[torch.Tensor], tokens: int,
-              top: int) -> None:
-    """From router logits (float32 [tokens, >= experts], a product with float32 sums): chosen int32 [tokens, top] and
-    weights float32 [tokens, top], the ``top`` experts with the largest softmax(logits[:, :experts]) + correction and
-    their softmax scores divided by their sum; shared_gate float32 [tokens] = sigmoid(logits[:, gate_column])."""
+              top: int, bias: Optional[torch.Tensor] = None) -> None:
+    """From router logits (float32 [tokens, >= experts], a product with float32 sums; ``bias`` float32 [experts] is
+    added to them first): chosen int32 [tokens, top] and weights float32 [tokens, top], the ``top`` experts with the
+    largest softmax(logits[:, :experts]) + correction and their softmax scores divided by their sum (without a
+    correction that is: the largest logits choose, and the weights are the softmax over the chosen logits alone);
+    shared_gate float32 [tokens] = sigmoid(logits[:, gate_column])."""
     _need(chosen, torch.int32, "chosen")
     _need(weights, torch.float32, "weights")
     assert logits.dtype == torch.float32 and logits.stride(-1) == 1 and logits.shape[-1] >= experts
-    _check(library().celeg_moe_route(_ptr(logits), logits.stride(0), _ptr(correction),
+    if bias is not None:
+        _need(bias, torch.float32, "bias")
+        assert bias.numel() >= experts
+    _check(library().celeg_moe_route(_ptr(logits), logits.stride(0), _ptr(bias), _ptr(correction),
                                      -1 if gate_column is None else gate_column, _ptr(chosen), _ptr(weights),
                                      _ptr(shared_gate), tokens, experts, top, _stream()))
 

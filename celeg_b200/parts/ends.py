@@ -28,22 +28,35 @@ from .runtime import Runtime, StepContext
 
 @register_part("input", "embedding")
 class EmbeddingInput:
-    """rows = multiplier * table[token ids] in float32; the first half of the first block's norm when asked."""
+    """rows = multiplier * table[token ids] in float32; the first half of the first block's norm when asked.
+    With ``sinusoid_base`` b a vector of the token's position p is added (Vaswani et al., "Attention Is All You
+    Need", 2017, with sine and cosine side by side instead of in two halves): entry 2i is sin(p b^(-2i / width)),
+    entry 2i + 1 the cosine of the same angle; the frequencies are made in float64 and kept in float32, the angle
+    is a float32 product."""
 
     def __init__(self, params: Mapping, weights: Mapping[str, torch.Tensor], parts: Mapping, rt: Runtime):
         self.rt = rt
         self.table = rt.matrix(weights["table"])
         self.vocab_size = int(self.table.shape[0])
         self.multiplier = float(params.get("multiplier", 1.0))
+        base = params.get("sinusoid_base")
+        self.frequencies = None
+        if base is not None:
+            width = int(self.table.shape[1])
+            pairs = torch.arange((width + 1) // 2, dtype=torch.float64)
+            self.frequencies = torch.pow(torch.tensor(float(base), dtype=torch.float64), -2.0 * pairs / width).to(
+                device=rt.device, dtype=torch.float32)
 
     def run(self, stream, step: StepContext, first=None) -> None:
         tokens = step.token_ids[:step.tokens]
+        places = {} if self.frequencies is None else {"positions": step.positions, "frequencies": self.frequencies}
         if first is not None:
             norm, (weight, split) = first
-            kernels.embedding(self.table, tokens, stream.residual, self.multiplier, prepare=split, next_weight=weight)
+            kernels.embedding(self.table, tokens, stream.residual, self.multiplier, prepare=split, next_weight=weight,
+                              **places)
             stream.prepared = (norm, split)
         else:
-            kernels.embedding(self.table, tokens, stream.residual, self.multiplier)
+            kernels.embedding(self.table, tokens, stream.residual, self.multiplier, **places)
 
 
 @register_part("output", "norm_head")

@@ -142,6 +142,9 @@ class PagedAttentionKernels:
         among the query heads of a group and splits long contexts, where a prompt kernel would walk the whole
         context once per query head for one row of a 128-row tile."""
         rt = self.rt
+        if self._values_differ():
+            self._attend_general(step, table, 0)
+            return
         if self._decodes(step):
             self._attend_single_tokens(step, table, step.tokens)
             return
@@ -188,10 +191,21 @@ class PagedAttentionKernels:
                                       self.head_dim, b.page_tokens, self.window, self.scale, step.error_flag,
                                       sinks=self.sinks)
             return
-        kernels.attention_generic(self.qkv[skip:], self.qkv_width, self.attended[skip:], b.k, values,
+        self._attend_general(step, table, skip)
+
+    def _values_differ(self) -> bool:
+        """Values of another size than the keys: only the general kernel reads those."""
+        return getattr(self, "value_dim", None) not in (None, self.head_dim)
+
+    def _attend_general(self, step: StepContext, table: torch.Tensor, skip: int) -> None:
+        """The tokens from ``skip`` on through the general kernel: a warp a (token, query head), any sizes, a window
+        or a chunked mask (``chunk``), values of their own size (``value_dim``)."""
+        b = self.binding
+        kernels.attention_generic(self.qkv[skip:], self.qkv_width, self.attended[skip:], b.k, self._value_cache(),
                                   step.positions[skip:], step.token_span[skip:], table, step.tokens - skip,
                                   self.heads, self.kv_heads, self.head_dim, b.page_tokens, self.window, self.scale,
-                                  step.error_flag, sinks=self.sinks)
+                                  step.error_flag, sinks=self.sinks, value_dim=getattr(self, "value_dim", None),
+                                  chunk=getattr(self, "chunk", None))
 
 
 @register_part("mixer", "attention")
@@ -315,6 +329,142 @@ class AttentionMixer(PagedAttentionKernels):
                                            b.page_tokens, self.eps, True, step.error_flag)
         self.attend(step, table)
         rt.linear(self.attended, self.w_out, out, t)
+
+
+@register_part("mixer", "chunked_attention")
+class ChunkedAttentionMixer(PagedAttentionKernels):
+    """Causal grouped-query softmax attention without any position encoding, with optional biases on its four
+    projections (tensors ``q_bias``, ``k_bias``, ``v_bias``, ``out_bias``), values of a size ``vdim`` of their own, a
+    softmax scale given by the configuration, and an optional chunked mask: with ``chunk`` = c a query at position i
+    reads key j <= i only if floor(i / c) = floor(j / c), chunks counted from position 0 of the sequence (so the mask
+    does not depend on how a prompt was cut into steps). Query head h reads key/value head h // (heads / kv_heads).
+
+    One fused [q | k | v] projection leaves float32 sums; one launch adds the biases, rounds once and writes q to its
+    buffer and k and v to the paged cache. On the bfloat16 path, when keys and values differ in size and the
+    tensor-core kernels take the larger size, both are stored at that size (the tails zero: a zero adds nothing to a
+    score, and a zero value column gives a zero result column, which meets zero columns of the output projection);
+    otherwise heads are stored as they are and the general kernel reads values of their own size."""
+
+    def __init__(self, params: Mapping, weights: Mapping[str, torch.Tensor], parts: Mapping, rt: Runtime):
+        self.rt = rt
+        self.hidden = int(params["hidden_size"])
+        self.heads = int(params["heads"])
+        self.kv_heads = int(params.get("kv_heads") or self.heads)
+        self.dim = int(params["dim"])
+        self.vdim = int(params.get("vdim") or self.dim)
+        self.scale = float(params.get("scale", self.dim ** -0.5))
+        chunk = params.get("chunk")
+        self.chunk = int(chunk) if chunk else None
+        if self.chunk is not None and self.chunk < 1:
+            raise ValueError(f"chunked_attention: a chunk of {self.chunk} positions")
+        if self.heads % self.kv_heads:
+            raise ValueError(f"{self.heads} query heads are not a multiple of {self.kv_heads} kv heads")
+        self.window = None
+        self.sinks = None
+        # sizes of a stored head: what the kernels see as head size (keys, queries) and value size
+        self.head_dim = self.value_dim = None
+        larger = max(self.dim, self.vdim)
+        if self.dim == self.vdim or (rt.act_dtype == torch.bfloat16 and self._fast_kernels_take(larger)):
+            self.head_dim = self.value_dim = larger
+        else:
+            self.head_dim, self.value_dim = self.dim, self.vdim
+        q_width, k_width, v_width = self.heads * self.dim, self.kv_heads * self.dim, self.kv_heads * self.vdim
+        self.w_qkv = rt.matrix(torch.cat([weights["q"], weights["k"], weights["v"]], dim=0))
+        biases = [weights.get("q_bias"), weights.get("k_bias"), weights.get("v_bias")]
+        if any(b is not None for b in biases):
+            widths = (q_width, k_width, v_width)
+            self.bias = rt.vector(torch.cat([b.float() if b is not None else torch.zeros(w) for b, w in zip(biases, widths)]))
+        else:
+            self.bias = None
+        w_out = weights["out"]
+        if self.value_dim != self.vdim:          # zero columns where the attention's result has its zero tail
+            padded = torch.zeros((w_out.shape[0], self.heads, self.value_dim), dtype=w_out.dtype)
+            padded[:, :, :self.vdim] = w_out.reshape(w_out.shape[0], self.heads, self.vdim)
+            w_out = padded.reshape(w_out.shape[0], self.heads * self.value_dim)
+        self.w_out = rt.matrix(w_out)
+        self.out_bias = rt.vector(weights["out_bias"]) if "out_bias" in weights else None
+        self.binding: Optional[PagedBinding] = None
+        self._resident_blocks: Optional[int] = None
+        self.projected = rt.scratch("chunked_attention.proj", q_width + k_width + v_width, torch.float32)
+        self.qkv_width = self.heads * self.head_dim
+        self.qkv = rt.scratch("chunked_attention.q", self.qkv_width)
+        self.attended = rt.scratch("chunked_attention.out", self.heads * self.value_dim)
+        self.unbiased = rt.scratch("chunked_attention.unbiased", self.hidden, torch.float32) if self.out_bias is not None else None
+
+    def _fast_kernels_take(self, size: int) -> bool:
+        return (kernels.attention_prefill_supported(self.heads, self.kv_heads, size, torch.bfloat16)
+                and kernels.attention_decode_supported(self.heads, self.kv_heads, size, torch.bfloat16))
+
+    def cache_need(self):
+        return PagedNeed(kv_heads=self.kv_heads, head_dim=self.head_dim, window=None,
+                         value_head_dim=None if self.value_dim == self.head_dim else self.value_dim)
+
+    def bind_cache(self, binding: PagedBinding) -> None:
+        if not binding.owner:
+            raise ValueError("chunked_attention writes its keys and values: it cannot read another position's cache")
+        self.binding = binding
+
+    def _attend(self, x: torch.Tensor, step: StepContext) -> None:
+        rt, b, t = self.rt, self.binding, step.tokens
+        rt.linear(x, self.w_qkv, self.projected, t)
+        table = step.block_tables[b.group]
+        kernels.bias_store_kv(self.projected, self.bias, self.qkv, step.positions, step.token_span, table, b.k, b.v, t,
+                              self.heads, self.kv_heads, self.dim, self.vdim, self.head_dim, self.value_dim,
+                              b.page_tokens, step.error_flag)
+        self.attend(step, table)
+
+    def forward_without_bias(self, x: torch.Tensor, out: torch.Tensor, step: StepContext) -> Optional[torch.Tensor]:
+        """forward() into a float32 ``out`` without the output projection's bias, which is returned (or None) for a
+        caller that adds it in a pass of its own."""
+        self._attend(x, step)
+        self.rt.linear(self.attended, self.w_out, out, step.tokens)
+        return self.out_bias
+
+    def forward(self, x: torch.Tensor, out: torch.Tensor, step: StepContext) -> None:
+        if self.out_bias is None:
+            self._attend(x, step)
+            self.rt.linear(self.attended, self.w_out, out, step.tokens)
+            return
+        self.forward_without_bias(x, self.unbiased, step)
+        kernels.scaled_sum(self.unbiased, None, self.out_bias, 1.0, 0.0, out, step.tokens)
+
+
+@register_part("mixer", "side_by_side")
+class SideBySideMixer:
+    """Two mixers (nested parts ``left`` and ``right``) that read the same rows; the result is
+    left_scale * left + right_scale * right. Each child leaves its result as float32 rows (its last product's sums);
+    one launch scales, adds (a child's output bias too, if it hands one over) and rounds once. A child that holds
+    a cache gets its own: the children are named to the model under ``children``."""
+
+    def __init__(self, params: Mapping, weights: Mapping[str, torch.Tensor], parts: Mapping, rt: Runtime):
+        self.rt = rt
+        self.hidden = int(params["hidden_size"])
+        self.left_scale = float(params.get("left_scale", 1.0))
+        self.right_scale = float(params.get("right_scale", 1.0))
+        if parts.get("left") is None or parts.get("right") is None:
+            raise ValueError("side_by_side: needs the nested mixers 'left' and 'right'")
+        self.left, self.right = parts["left"], parts["right"]
+        self.children = {"left": self.left, "right": self.right}
+        self.left_out = rt.scratch("side_by_side.left", self.hidden, torch.float32)
+        self.right_out = rt.scratch("side_by_side.right", self.hidden, torch.float32)
+
+    @staticmethod
+    def _run(child, x, out, step):
+        without = getattr(child, "forward_without_bias", None)
+        if without is not None:
+            return without(x, out, step)
+        child.forward(x, out, step)
+        return None
+
+    def forward(self, x: torch.Tensor, out: torch.Tensor, step: StepContext) -> None:
+        left_bias = self._run(self.left, x, self.left_out, step)
+        right_bias = self._run(self.right, x, self.right_out, step)
+        if right_bias is not None and left_bias is None:
+            kernels.scaled_sum(self.right_out, self.left_out, right_bias, self.right_scale, self.left_scale, out, step.tokens)
+            return
+        if right_bias is not None:
+            kernels.scaled_sum(self.right_out, None, right_bias, 1.0, 0.0, self.right_out, step.tokens)
+        kernels.scaled_sum(self.left_out, self.right_out, left_bias, self.left_scale, self.right_scale, out, step.tokens)
 
 
 @register_part("mixer", "short_conv")

@@ -28,12 +28,16 @@ from .runtime import Runtime
 @register_part("norm", "rmsnorm")
 class RmsNorm:
     """y = x / sqrt(mean(x^2) + eps) * w, the weight a direct scale
-    (celeg src/backend/cpu/kernels/elementwise.cpp:56-76)."""
+    (celeg src/backend/cpu/kernels/elementwise.cpp:56-76). With ``weight_offset`` c the stored tensor lies around
+    zero and stands for the scale c + w (the sum is made once, in float32, when the part is built)."""
 
     def __init__(self, params: Mapping, weights: Mapping[str, torch.Tensor], rt: Runtime):
         self.width = int(params["width"])
         self.eps = float(params["eps"])
         self.weight = rt.vector(weights["weight"])
+        offset = float(params.get("weight_offset", 0.0))
+        if offset != 0.0:
+            self.weight.add_(offset)
         if self.weight.shape != (self.width,):
             raise ValueError(f"rmsnorm weight has shape {tuple(self.weight.shape)}, expected ({self.width},)")
 
