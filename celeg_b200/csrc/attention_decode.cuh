@@ -157,7 +157,7 @@ __device__ __forceinline__ void attention_decode_item(const DecodeParams& p, con
     const int group = p.q_heads / p.kv_heads;
     const int d = p.head_dim;
     const int pos = p.positions[t];
-    const int first = p.window > 0 ? max(0, pos - p.window + 1) : 0;
+    const int first = first_visible_key(pos, p.window);
     const int total = pos + 1 - first;
     const int n_splits = (total + p.chunk - 1) / p.chunk;
     if (n_splits > p.max_splits) {
@@ -589,7 +589,7 @@ __device__ __forceinline__ void attention_decode_item_solo(const DecodeParams& p
     const int group = p.q_heads / p.kv_heads;
     const int d = p.head_dim;
     const int pos = p.positions[t];
-    const int first = p.window > 0 ? max(0, pos - p.window + 1) : 0;
+    const int first = first_visible_key(pos, p.window);
     const int end = pos + 1;
     if (end - first > p.chunk) {
         // more keys than the launch was laid out for (one split): nothing is written, the caller reads code 3

@@ -107,7 +107,7 @@ __global__ void __launch_bounds__(kPrefillThreads, D_PAD <= 64 ? 2 : 1) attentio
     float run_max[2] = {sink_log2, sink_log2};
     float run_sum[2] = {sink_one, sink_one};
 
-    const int first_key = p.window > 0 ? max(0, pos0 - p.window + 1) : 0;
+    const int first_key = first_visible_key(pos0, p.window);
     const int q_row = warp * 16 + g;                 // this thread's first row; the second is q_row + 8
 
     // asynchronous copy of the key/value tile `kb` into stage `stage`; keys outside [first_key, pos_last] are zeros
@@ -179,7 +179,7 @@ __global__ void __launch_bounds__(kPrefillThreads, D_PAD <= 64 ? 2 : 1) attentio
         float tile_max[2] = {-INFINITY, -INFINITY};
         const int warp_first_pos = pos0 + warp * 16;
         const bool full_tile = kb * kBlockN + kBlockN - 1 <= warp_first_pos && warp * 16 + 15 < rows &&
-                               (p.window <= 0 || kb * kBlockN > warp_first_pos + 15 - p.window);
+                               kb * kBlockN >= first_visible_key(warp_first_pos + 15, p.window);
         if (full_tile) {
 #pragma unroll
             for (int nt = 0; nt < kBlockN / 8; ++nt) {
@@ -198,7 +198,7 @@ __global__ void __launch_bounds__(kPrefillThreads, D_PAD <= 64 ? 2 : 1) attentio
                     const int row = q_row + (e >> 1) * 8;
                     const int key = kb * kBlockN + nt * 8 + c2 + (e & 1);
                     const int qpos = pos0 + row;
-                    const bool valid = row < rows && key <= qpos && (p.window <= 0 || key > qpos - p.window);
+                    const bool valid = row < rows && key <= qpos && key >= first_visible_key(qpos, p.window);
                     const float v = valid ? s[nt][e] * p.scale_log2 : -INFINITY;
                     s[nt][e] = v;
                     tile_max[e >> 1] = fmaxf(tile_max[e >> 1], v);

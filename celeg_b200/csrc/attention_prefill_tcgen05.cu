@@ -128,7 +128,7 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
         const int rows = min(kFaM, span_len - tile_first);
         const int pos0 = p.positions[t0];
         const int pos_last = pos0 + rows - 1;
-        const int first_key = p.window > 0 ? max(0, pos0 - p.window + 1) : 0;
+        const int first_key = first_visible_key(pos0, p.window);
         const int block_begin = first_key / kFaN;
         const int block_end = pos_last / kFaN + 1;
 
@@ -249,7 +249,7 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
                 tcgen05_fence_after();
                 const int key_base = (block_begin + i) * kFaN;
                 const bool full = key_base + kFaN - 1 <= pos0 && rows == kFaM &&
-                                  (p.window <= 0 || key_base > pos_last - p.window);
+                                  key_base >= first_visible_key(pos_last, p.window);
                 // the whole row of scores in registers (one pass over tensor memory), not yet scaled
                 float sc[kFaN];
                 {
@@ -266,7 +266,7 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
                 if (!full) {
                     // keys key_base + [lo, hi] are the ones this row sees
                     const int hi = live ? min(kFaN - 1, qpos - key_base) : -1;
-                    const int lo = p.window > 0 ? max(0, qpos - p.window + 1 - key_base) : 0;
+                    const int lo = first_visible_key(qpos, p.window) - key_base;
 #pragma unroll
                     for (int j = 0; j < kFaN; ++j) sc[j] = (j <= hi && j >= lo) ? sc[j] : -INFINITY;
                 }

@@ -19,6 +19,15 @@ template <> __device__ __forceinline__ __nv_bfloat16 from_float<__nv_bfloat16>(f
     return __float2bfloat16_rn(v);
 }
 
+// The first key that a query at position `pos` reads (the last one is `pos` itself). window > 0: the last `window`
+// positions; window < 0: the keys of its own chunk of -window positions, chunks counted from position 0 of the
+// sequence; 0: every earlier key. Not decreasing in `pos`.
+__host__ __device__ __forceinline__ int first_visible_key(int pos, int window) {
+    if (window > 0) return pos - window + 1 > 0 ? pos - window + 1 : 0;
+    if (window < 0) return pos - pos % (-window);
+    return 0;
+}
+
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
     for (int offset = 16; offset > 0; offset >>= 1) v += __shfl_xor_sync(0xffffffffu, v, offset);

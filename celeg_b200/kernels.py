@@ -372,7 +372,8 @@ def attention_decode(q: torch.Tensor, q_row_stride: int, out: torch.Tensor, k_ca
     """One query token per row, keys split into chunks of ``chunk``; scratch: partial_o float32
     [tokens*q_heads*max_splits*head_dim], partial_ml float32 [tokens*q_heads*max_splits*2],
     counters int32 [tokens*kv_heads] (zero before the first call, left zero by every call).
-    ``sinks``: as for :func:`attention_generic`."""
+    ``sinks``: as for :func:`attention_generic`. ``window`` = -c (negative) stands for a chunked mask: a query reads the
+    keys of its own chunk of c positions, chunks counted from position 0; the prompt kernels read it the same way."""
     assert partial_o.numel() >= tokens * q_heads * max_splits * head_dim
     assert partial_ml.numel() >= tokens * q_heads * max_splits * 2
     assert counters.numel() >= tokens * kv_heads

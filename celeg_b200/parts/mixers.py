@@ -114,14 +114,23 @@ class PagedAttentionKernels:
     def _value_cache(self) -> torch.Tensor:
         return self.binding.v
 
+    def _mask(self) -> Optional[int]:
+        """What the tensor-core kernels get as ``window``: the window, or for a mixer with a chunked mask
+        (``chunk`` positions a chunk) minus the chunk's size, which they read as "the keys of the query's own
+        chunk"."""
+        chunk = getattr(self, "chunk", None)
+        return -int(chunk) if chunk else self.window
+
     def _decode_split(self, step: StepContext, tokens: Optional[int] = None):
         """One query token per request: how the keys are split so that few requests still fill the GPU,
         and the scratch of the split (chunk, max_splits, partial outputs, maxima and sums, counters)."""
         rt = self.rt
         if self._resident_blocks is None:
             self._resident_blocks = kernels.attention_decode_resident_blocks(self.head_dim) or DECODE_RESIDENT_BLOCKS
+        # (a chunked mask shows a query at most a chunk's keys, as a window of that size would)
         chunk, max_splits, cap_splits = decode_split(tokens or step.tokens, self.kv_heads, step.context_bucket,
-                                                     self.window, rt.max_context, self._resident_blocks)
+                                                     getattr(self, "chunk", None) or self.window, rt.max_context,
+                                                     self._resident_blocks)
         rows = rt.max_requests * self.heads * cap_splits
         partial_o = rt.flat_scratch("attention.partial_o", rows * self.head_dim, torch.float32)
         partial_ml = rt.flat_scratch("attention.partial_ml", rows * 2, torch.float32)
@@ -162,7 +171,7 @@ class PagedAttentionKernels:
         chunk, max_splits, partial_o, partial_ml, counters = self._decode_split(step, count)
         kernels.attention_decode(self.qkv, self.qkv_width, self.attended, b.k, self._value_cache(), step.positions,
                                  step.token_span, table, count, self.heads, self.kv_heads,
-                                 self.head_dim, b.page_tokens, self.window, self.scale, chunk, max_splits,
+                                 self.head_dim, b.page_tokens, self._mask(), self.scale, chunk, max_splits,
                                  partial_o, partial_ml, counters, step.error_flag, sinks=self.sinks)
 
     def _attend_portions(self, step: StepContext, table: torch.Tensor, skip: int) -> None:
@@ -182,13 +191,13 @@ class PagedAttentionKernels:
             tiles = step.prompt_tile_bound or sum((length + 127) // 128 for length in lengths)
             kernels.attention_prefill_tcgen05(self.qkv, self.qkv_width, self.attended, b.k, values, step.positions,
                                               span_begin, span_table, step.tokens, spans, tiles, self.heads,
-                                              self.kv_heads, self.head_dim, b.page_tokens, self.window, self.scale,
+                                              self.kv_heads, self.head_dim, b.page_tokens, self._mask(), self.scale,
                                               step.error_flag, sinks=self.sinks)
             return
         if kernels.attention_prefill_supported(self.heads, self.kv_heads, self.head_dim, rt.act_dtype):
             kernels.attention_prefill(self.qkv, self.qkv_width, self.attended, b.k, values, step.positions,
                                       span_begin, span_table, step.tokens, spans, self.heads, self.kv_heads,
-                                      self.head_dim, b.page_tokens, self.window, self.scale, step.error_flag,
+                                      self.head_dim, b.page_tokens, self._mask(), self.scale, step.error_flag,
                                       sinks=self.sinks)
             return
         self._attend_general(step, table, skip)
