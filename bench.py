@@ -8,7 +8,7 @@ batch 1 and 64. Prints ONE JSON line.
                   [--prefill-tokens T] [--chunk C] [--kernel-times] [--no-cuda-graph]      one phase, a short record
   python bench.py --workload lfm2-700m|lfm2-350m [--requests N] [--new-tokens N] [--max-batched-tokens N]
                   [--prefill-chunk N] [--kernel-times]       a scheduler workload through Engine.submit/step/poll
-  python bench.py --design ramosun|kedesun [--design-size w1024|w2048] [--kernel-times]
+  python bench.py --design ramosun|kedesun|naselorn [--design-size w1024|w2048] [--kernel-times]
                   the Ramosun design beside the closest LFM2 model at equal size: prefill of 2,048 tokens, decode at batch 8
 
 A "step" is one decode step of the whole batch. ``value`` is timed on the device (CUDA events
@@ -196,7 +196,9 @@ class KernelTimer:
              "add_dyt", "add_to_residual", "join_stream_embedding", "activation", "softcap", "recurrent_scan",
              "mlstm_gates", "delta_prepare", "gated_head_norm", "qk_whole_norm_rope_store", "recurrent_decode",
              "depth_average", "latent_prepare", "head_project", "head_gate", "moe_route", "moe_group", "moe_gather_rows",
-             "expert_product", "expert_product_tcgen05", "expert_rows", "moe_combine", "retention_segmented")
+             "expert_product", "expert_product_tcgen05", "expert_rows", "moe_combine", "retention_segmented",
+             "retention_decode_raw", "activation_columns", "bias_store_kv", "scaled_sum", "glu", "lru_prepare",
+             "block_diagonal_product", "lru_scan", "lru_decode")
 
     def __init__(self):
         self.pairs = []
@@ -497,6 +499,26 @@ def kedesun_config(width: int, vocab: int) -> dict:
             "max_context": 8192}
 
 
+def naselorn_config(width: int, vocab: int) -> dict:
+    """Eight layers: lightning, lightning with experts, side-by-side (chunked attention beside the gated linear
+    recurrent unit), lightning with experts, twice. The lightning mixer has Kedesun's retention sizes (heads of 64
+    keys and 128 values); the attention has sixteenth-of-the-width many query heads of 128 on a quarter as many
+    key heads, chunks of 1,024 positions; the recurrent unit has as many channels as the model is wide, in blocks
+    of 128, behind four taps; the feed-forwards are Kedesun's."""
+    heads = width // 128
+    dense = {"kind": "dense", "ff": (8 * width // 3 + 127) // 128 * 128}
+    experts = {"kind": "moe", "router": {"experts": 32, "top": 4}, "expert": {"ff": width // 2}, "shared": {"ff": width}}
+    decay = [1.0 - 2.0 ** (-5.0 - 7.0 * head / max(heads - 1, 1)) for head in range(heads)]
+    lightning = {"type": "lightning", "mixer": {"heads": heads, "dim": 64, "vdim": 128, "decay": decay}}
+    parallel = {"type": "parallel", "mixer": {
+        "left": {"heads": width // 64 // 2, "kv_heads": max(width // 512, 1), "dim": 128, "vdim": 128, "scale": 128 ** -0.5,
+                 "mask": {"size": 1024}},
+        "right": {"width": width, "blocks": width // 128, "conv": 4}, "left_scale": 1.0, "right_scale": 1.0}}
+    run = [dict(lightning, mlp=dense), dict(lightning, mlp=experts), dict(parallel, mlp=dense), dict(lightning, mlp=experts)]
+    return {"architecture": "Naselorn", "vocab": vocab, "width": width, "norm": {"eps": 1e-5},
+            "embedding": {"scale": float(width) ** 0.5}, "layers": run + run, "max_context": 8192}
+
+
 def lfm2_relative(width: int, vocab: int) -> dict:
     raw = dict(LFM2_1P2B)
     # eight blocks like Ramosun's run order; a SwiGLU of 8/3 width has the parameters of a dense feed-forward of 4 width
@@ -521,6 +543,9 @@ def run_design(args) -> dict:
         entry = {}
         if args.design == "kedesun":     # beside both earlier designs: Ramosun has its block form and matrix states
             models = (("kedesun", kedesun_config(width, vocab)), ("ramosun", ramosun_config(width, vocab)),
+                      ("lfm2", lfm2_relative(width, vocab)))
+        elif args.design == "naselorn":  # beside Kedesun, whose layers it resembles most (fixed decays, experts)
+            models = (("naselorn", naselorn_config(width, vocab)), ("kedesun", kedesun_config(width, vocab)),
                       ("lfm2", lfm2_relative(width, vocab)))
         else:
             models = (("ramosun", ramosun_config(width, vocab)), ("lfm2", lfm2_relative(width, vocab)))
@@ -803,7 +828,7 @@ def main() -> int:
     parser.add_argument("--new-tokens", type=int, default=0, help="--workload: tokens to generate per request")
     parser.add_argument("--max-batched-tokens", type=int, default=0, help="--workload: token budget of a step")
     parser.add_argument("--prefill-chunk", type=int, default=0, help="--workload: longest prompt portion")
-    parser.add_argument("--design", default=None, choices=["ramosun", "kedesun"],
+    parser.add_argument("--design", default=None, choices=["ramosun", "kedesun", "naselorn"],
                         help="prefill and decode of that design beside the closest LFM2 model at equal size")
     parser.add_argument("--design-size", default=None, choices=sorted(DESIGN_SIZES), help="--design: one size only")
     parser.add_argument("--no-warmup-run", action="store_true",
