@@ -182,16 +182,21 @@ __device__ __forceinline__ void lru_cp_async_16(void* smem, const void* global) 
 // The scan: S <- a S + b per channel along a span, out = S y'. A block takes kLruChannels channels of one span; the
 // tokens' a, b and y' arrive in tiles of kLruTile tokens through a ring of kLruStages stages (cp.async), so that the
 // only thing a token waits for is the multiply-add of the token before it.
-constexpr int kLruChannels = 64, kLruTile = 16, kLruStages = 3;
+// A warp a block and twelve stages: a token costs the chain about ten cycles, a tile of sixteen well under the time a
+// copy from memory takes, so eleven tiles are under way while one is walked.
+constexpr int kLruChannels = 32, kLruTile = 16, kLruStages = 12;
+constexpr size_t kLruScanSmem = 3ull * kLruStages * kLruTile * kLruChannels * sizeof(float);
 template <typename A>
 __global__ void __launch_bounds__(kLruChannels) lru_scan_kernel(const float* __restrict__ gates,
                                                                 const float* __restrict__ y, A* __restrict__ out,
                                                                 float* state, long long slot_stride,
                                                                 const int* span_begin, const int* span_slot, int width,
                                                                 int vector_copies) {
-    __shared__ __align__(16) float a_s[kLruStages][kLruTile][kLruChannels];
-    __shared__ __align__(16) float b_s[kLruStages][kLruTile][kLruChannels];
-    __shared__ __align__(16) float y_s[kLruStages][kLruTile][kLruChannels];
+    extern __shared__ __align__(16) float lru_scan_smem[];
+    typedef float (*Ring)[kLruTile][kLruChannels];
+    Ring a_s = reinterpret_cast<Ring>(lru_scan_smem);
+    Ring b_s = a_s + kLruStages;
+    Ring y_s = b_s + kLruStages;
     chain_release();
     chain_wait();
     const int span = blockIdx.y, c0 = blockIdx.x * kLruChannels, tid = threadIdx.x;
@@ -295,13 +300,29 @@ __global__ void __launch_bounds__(256) lru_decode_kernel(const LruDecodeArgs p) 
     }
     __syncthreads();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
-    for (int o = warp; o < 2 * part; o += warps) {
-        const int gate = o / part, j = o % part;
-        const float* w = p.gate_w + (((size_t)gate * p.blocks + part_index) * part + j) * part;
-        float sum = 0.0f;
-        for (int i = lane; i < part; i += 32) sum = fmaf(w[i], u_s[i], sum);
-        sum = warp_sum(sum);
-        if (lane == 0) g_s[o] = sum;
+    // eight outputs a round, so that eight rows of the matrices are under way at once (each output's sum as before:
+    // a lane its strided inputs in ascending order, then the warp's sum)
+    constexpr int kOutputs = 8;
+    for (int o0 = warp * kOutputs; o0 < 2 * part; o0 += warps * kOutputs) {
+        const float* w[kOutputs];
+        float sums[kOutputs];
+#pragma unroll
+        for (int q = 0; q < kOutputs; ++q) {
+            const int o = min(o0 + q, 2 * part - 1);
+            const int gate = o / part, j = o % part;
+            w[q] = p.gate_w + (((size_t)gate * p.blocks + part_index) * part + j) * part;
+            sums[q] = 0.0f;
+        }
+        for (int i = lane; i < part; i += 32) {
+            const float uv = u_s[i];
+#pragma unroll
+            for (int q = 0; q < kOutputs; ++q) sums[q] = fmaf(w[q][i], uv, sums[q]);
+        }
+#pragma unroll
+        for (int q = 0; q < kOutputs; ++q) {
+            const float sum = warp_sum(sums[q]);
+            if (lane == 0 && o0 + q < 2 * part) g_s[o0 + q] = sum;
+        }
     }
     __syncthreads();
     A* dst = static_cast<A*>(p.out) + (size_t)t * width;
@@ -377,11 +398,18 @@ CELEG_API int celeg_lru_scan(float* gates, const float* u, const float* gate_bia
     if (status != 0) return status;
     const int vector_copies = width % 4 == 0 && (((size_t)gates | (size_t)y) & 15) == 0;
     dim3 grid((width + kLruChannels - 1) / kLruChannels, spans);
+    static bool sized = false;
+    if (!sized) {
+        if (cudaFuncSetAttribute(lru_scan_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kLruScanSmem) != cudaSuccess ||
+            cudaFuncSetAttribute(lru_scan_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kLruScanSmem) != cudaSuccess)
+            CELEG_REQUIRE(false, "lru_scan: %zu bytes of shared memory were refused", kLruScanSmem);
+        sized = true;
+    }
     if (act_dtype == kFloat32)
-        launch_chained(lru_scan_kernel<float>, grid, kLruChannels, 0, stream, (const float*)gates, y, (float*)out, state,
+        launch_chained(lru_scan_kernel<float>, grid, kLruChannels, kLruScanSmem, stream, (const float*)gates, y, (float*)out, state,
                        slot_stride, span_begin, span_slot, width, vector_copies);
     else
-        launch_chained(lru_scan_kernel<__nv_bfloat16>, grid, kLruChannels, 0, stream, (const float*)gates, y,
+        launch_chained(lru_scan_kernel<__nv_bfloat16>, grid, kLruChannels, kLruScanSmem, stream, (const float*)gates, y,
                        (__nv_bfloat16*)out, state, slot_stride, span_begin, span_slot, width, vector_copies);
     return check_launch("lru_scan");
 }

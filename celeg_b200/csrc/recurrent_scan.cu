@@ -394,6 +394,55 @@ __global__ void gated_head_norm_kernel(const float* o, const float* gate, int ga
     }
 }
 
+// The same for wide units (one norm over all heads' columns together): a block per (token, head), 16-byte reads
+// where the rows allow them. The order of the sum differs from the warp's; both are float32 sums of the same squares.
+template <typename A>
+__global__ void __launch_bounds__(256) gated_row_norm_kernel(const float* o, const float* gate, int gate_stride,
+                                                             const float* weight, int weight_per_head, A* out, int heads,
+                                                             int vdim, float eps, int gate_kind, int vectors) {
+    __shared__ float partial[8];
+    chain_release();
+    chain_wait();
+    const long long unit = blockIdx.x;
+    const int t = (int)(unit / heads), h = (int)(unit % heads);
+    const float* src = o + ((size_t)t * heads + h) * vdim;
+    const float* w = weight ? weight + (weight_per_head ? (size_t)h * vdim : 0) : nullptr;
+    const float* g = gate + (size_t)t * gate_stride + (size_t)h * vdim;
+    A* dst = out + ((size_t)t * heads + h) * vdim;
+    float sum = 0.0f;
+    if (vectors) {
+        for (int i = threadIdx.x * 4; i < vdim; i += blockDim.x * 4) {
+            const float4 v = *reinterpret_cast<const float4*>(src + i);
+            sum += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+        }
+    } else {
+        for (int i = threadIdx.x; i < vdim; i += blockDim.x) sum += src[i] * src[i];
+    }
+    sum = warp_sum(sum);
+    if ((threadIdx.x & 31) == 0) partial[threadIdx.x >> 5] = sum;
+    __syncthreads();
+    sum = 0.0f;
+    for (int k = 0; k < (int)(blockDim.x >> 5); ++k) sum += partial[k];      // (every thread adds in the same order)
+    const float inv = 1.0f / sqrtf(sum / (float)vdim + eps);
+    auto one = [&](float x, float z, float scale) {
+        const float sig = 1.0f / (1.0f + expf(-z));
+        return x * inv * scale * (gate_kind == 0 ? sig : z * sig);
+    };
+    if (vectors) {
+        for (int i = threadIdx.x * 4; i < vdim; i += blockDim.x * 4) {
+            const float4 v = *reinterpret_cast<const float4*>(src + i);
+            const float4 z = *reinterpret_cast<const float4*>(g + i);
+            const float4 s = w ? *reinterpret_cast<const float4*>(w + i) : make_float4(1.0f, 1.0f, 1.0f, 1.0f);
+            dst[i] = from_float<A>(one(v.x, z.x, s.x));
+            dst[i + 1] = from_float<A>(one(v.y, z.y, s.y));
+            dst[i + 2] = from_float<A>(one(v.z, z.z, s.z));
+            dst[i + 3] = from_float<A>(one(v.w, z.w, s.w));
+        }
+    } else {
+        for (int i = threadIdx.x; i < vdim; i += blockDim.x) dst[i] = from_float<A>(one(src[i], g[i], w ? w[i] : 1.0f));
+    }
+}
+
 // ---------------------------------------------------------------------------------------------------------
 // Decoding: every request brings one token. One block per (request, head) does everything between the input
 // projection and the output projection: the delta rule's short convolutions over the carried inputs with SiLU,
@@ -925,6 +974,19 @@ CELEG_API int celeg_gated_head_norm(const float* o, const float* gate, int gate_
                   gate_kind);
     if (tokens == 0) return 0;
     const long long units = (long long)tokens * heads;
+    if (vdim >= 512) {          // a unit is worth a block
+        CELEG_REQUIRE(units <= 0x7fffffffLL, "gated_head_norm: %lld units exceed one launch", units);
+        const int vectors = vdim % 4 == 0 && gate_stride % 4 == 0 && ((uintptr_t)o | (uintptr_t)gate | (uintptr_t)weight) % 16 == 0;
+        if (act_dtype == kFloat32)
+            launch_chained(gated_row_norm_kernel<float>, (unsigned)units, 256, 0, stream, o, gate, gate_stride, weight,
+                           weight_per_head, (float*)out, heads, vdim, eps, gate_kind, vectors);
+        else if (act_dtype == kBFloat16)
+            launch_chained(gated_row_norm_kernel<__nv_bfloat16>, (unsigned)units, 256, 0, stream, o, gate, gate_stride,
+                           weight, weight_per_head, (__nv_bfloat16*)out, heads, vdim, eps, gate_kind, vectors);
+        else
+            CELEG_REQUIRE(false, "gated_head_norm: unknown dtype code %d", act_dtype);
+        return check_launch("gated_head_norm");
+    }
     const unsigned blocks = (unsigned)((units + 3) / 4);
     if (act_dtype == kFloat32)
         launch_chained(gated_head_norm_kernel<float>, blocks, 128, 0, stream, o, gate, gate_stride, weight,
