@@ -13,7 +13,7 @@
 //
 // Prompt portions: four launches (branches and convolution; the carried inputs; the gates' products, a batched
 // FFMA product over the parts; decays and inputs element by element; the scan, a thread per channel walking its
-// span over tiles staged in shared memory, so that the chain per token is one multiply-add). Steps in which every
+// span over tiles that other warps stage in shared memory, so that the chain per token is one multiply-add). Steps in which every
 // request brings one token: one launch, a block per (request, part).
 #include "common.cuh"
 
@@ -182,16 +182,17 @@ __device__ __forceinline__ void lru_cp_async_16(void* smem, const void* global) 
 // The scan: S <- a S + b per channel along a span, out = S y'. A block takes kLruChannels channels of one span; the
 // tokens' a, b and y' arrive in tiles of kLruTile tokens through a ring of kLruStages stages (cp.async), so that the
 // only thing a token waits for is the multiply-add of the token before it.
-// A warp a block and twelve stages: a token costs the chain about ten cycles, a tile of sixteen well under the time a
-// copy from memory takes, so eleven tiles are under way while one is walked.
-constexpr int kLruChannels = 32, kLruTile = 16, kLruStages = 12;
+// One warp walks the chain of its 32 channels; three more warps of the block do nothing but copy (one the decays, one
+// the inputs, one the y branch), so that the walking warp issues little besides the tile's loads from shared memory,
+// its sixteen multiply-adds and its stores. Eight stages: seven tiles are under way while one is walked.
+constexpr int kLruChannels = 32, kLruTile = 16, kLruStages = 8, kLruScanThreads = 128;
 constexpr size_t kLruScanSmem = 3ull * kLruStages * kLruTile * kLruChannels * sizeof(float);
 template <typename A>
-__global__ void __launch_bounds__(kLruChannels) lru_scan_kernel(const float* __restrict__ gates,
-                                                                const float* __restrict__ y, A* __restrict__ out,
-                                                                float* state, long long slot_stride,
-                                                                const int* span_begin, const int* span_slot, int width,
-                                                                int vector_copies) {
+__global__ void __launch_bounds__(kLruScanThreads) lru_scan_kernel(const float* __restrict__ gates,
+                                                                   const float* __restrict__ y, A* __restrict__ out,
+                                                                   float* state, long long slot_stride,
+                                                                   const int* span_begin, const int* span_slot, int width,
+                                                                   int vector_copies) {
     extern __shared__ __align__(16) float lru_scan_smem[];
     typedef float (*Ring)[kLruTile][kLruChannels];
     Ring a_s = reinterpret_cast<Ring>(lru_scan_smem);
@@ -199,57 +200,80 @@ __global__ void __launch_bounds__(kLruChannels) lru_scan_kernel(const float* __r
     Ring y_s = b_s + kLruStages;
     chain_release();
     chain_wait();
-    const int span = blockIdx.y, c0 = blockIdx.x * kLruChannels, tid = threadIdx.x;
+    const int span = blockIdx.y, c0 = blockIdx.x * kLruChannels;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int t_begin = span_begin[span], t_end = span_begin[span + 1];
     if (t_end <= t_begin) return;
-    const int c = c0 + tid;
-    const bool live = c < width;
+    const int c = c0 + lane;
+    const bool walker = warp == 0, live = c < width;
     const int channels = min(kLruChannels, width - c0);
     float* cell = state + (long long)span_slot[span] * slot_stride + c;
-    float s = live ? *cell : 0.0f;
+    float s = walker && live ? *cell : 0.0f;
+    // what a copying warp copies: rows of `ld` floats from `src` into `ring`
+    const float* src = warp == 3 ? y + c0 : gates + (warp == 2 ? width : 0) + c0;
+    const size_t ld = warp == 3 ? (size_t)width : 2 * (size_t)width;
+    Ring ring = warp == 3 ? y_s : (warp == 2 ? b_s : a_s);
     auto issue = [&](int t0, int stage) {
         const int count = min(kLruTile, t_end - t0);
         if (count > 0) {
-            if (vector_copies) {
+            if (vector_copies && channels == kLruChannels) {          // eight copies of 16 bytes a row, four a lane
+#pragma unroll
+                for (int i = lane; i < kLruTile * 8; i += 32) {
+                    const int tt = i >> 3, e = (i & 7) << 2;
+                    if (tt < count) lru_cp_async_16(&ring[stage][tt][e], src + (size_t)(t0 + tt) * ld + e);
+                }
+            } else if (vector_copies) {
                 const int quads = channels >> 2;           // (width % 4 == 0, so channels % 4 == 0)
-                for (int i = tid; i < count * quads; i += kLruChannels) {
+                for (int i = lane; i < count * quads; i += 32) {
                     const int tt = i / quads, e = (i - tt * quads) << 2;
-                    const size_t row = (size_t)(t0 + tt);
-                    lru_cp_async_16(&a_s[stage][tt][e], gates + row * 2 * width + c0 + e);
-                    lru_cp_async_16(&b_s[stage][tt][e], gates + row * 2 * width + width + c0 + e);
-                    lru_cp_async_16(&y_s[stage][tt][e], y + row * width + c0 + e);
+                    lru_cp_async_16(&ring[stage][tt][e], src + (size_t)(t0 + tt) * ld + e);
                 }
             } else {
-                for (int i = tid; i < count * channels; i += kLruChannels) {
+                for (int i = lane; i < count * channels; i += 32) {
                     const int tt = i / channels, e = i - tt * channels;
-                    const size_t row = (size_t)(t0 + tt);
-                    lru_cp_async_4(&a_s[stage][tt][e], gates + row * 2 * width + c0 + e);
-                    lru_cp_async_4(&b_s[stage][tt][e], gates + row * 2 * width + width + c0 + e);
-                    lru_cp_async_4(&y_s[stage][tt][e], y + row * width + c0 + e);
+                    lru_cp_async_4(&ring[stage][tt][e], src + (size_t)(t0 + tt) * ld + e);
                 }
             }
         }
         asm volatile("cp.async.commit_group;\n" ::: "memory");       // (an empty group keeps the count of groups even)
     };
+    if (!walker) {
 #pragma unroll
-    for (int ahead = 0; ahead < kLruStages - 1; ++ahead) issue(t_begin + ahead * kLruTile, ahead);
+        for (int ahead = 0; ahead < kLruStages - 1; ++ahead) issue(t_begin + ahead * kLruTile, ahead);
+    }
     int stage = 0;
     for (int t0 = t_begin; t0 < t_end; t0 += kLruTile) {
-        issue(t0 + (kLruStages - 1) * kLruTile, (stage + kLruStages - 1) % kLruStages);
-        asm volatile("cp.async.wait_group %0;\n" ::"n"(kLruStages - 1) : "memory");
+        if (!walker) asm volatile("cp.async.wait_group %0;\n" ::"n"(kLruStages - 2) : "memory");
+        // one barrier a tile: behind it this tile's copies have landed, and the walking warp is done with the tile
+        // before, whose stage the copying warps fill next while this tile is walked
         __syncthreads();
+        if (!walker) issue(t0 + (kLruStages - 1) * kLruTile, (stage + kLruStages - 1) % kLruStages);
         const int count = min(kLruTile, t_end - t0);
-        if (live) {
-#pragma unroll 4
-            for (int tt = 0; tt < count; ++tt) {
-                s = fmaf(a_s[stage][tt][tid], s, b_s[stage][tt][tid]);
-                out[(size_t)(t0 + tt) * width + c] = from_float<A>(s * y_s[stage][tt][tid]);
+        if (walker && live) {
+            A* dst = out + (size_t)t0 * width + c;
+            if (count == kLruTile) {
+                float av[kLruTile], bv[kLruTile], yv[kLruTile];
+#pragma unroll
+                for (int tt = 0; tt < kLruTile; ++tt) {
+                    av[tt] = a_s[stage][tt][lane];
+                    bv[tt] = b_s[stage][tt][lane];
+                    yv[tt] = y_s[stage][tt][lane];
+                }
+#pragma unroll
+                for (int tt = 0; tt < kLruTile; ++tt) {
+                    s = fmaf(av[tt], s, bv[tt]);
+                    dst[(size_t)tt * width] = from_float<A>(s * yv[tt]);
+                }
+            } else {
+                for (int tt = 0; tt < count; ++tt) {
+                    s = fmaf(a_s[stage][tt][lane], s, b_s[stage][tt][lane]);
+                    dst[(size_t)tt * width] = from_float<A>(s * y_s[stage][tt][lane]);
+                }
             }
         }
-        __syncthreads();                                 // the stage is free for the tile that is issued next
         stage = (stage + 1) % kLruStages;
     }
-    if (live) *cell = s;
+    if (walker && live) *cell = s;
 }
 
 // Decoding: every request brings one token. A block takes one part of one request's channels and does everything
@@ -406,10 +430,10 @@ CELEG_API int celeg_lru_scan(float* gates, const float* u, const float* gate_bia
         sized = true;
     }
     if (act_dtype == kFloat32)
-        launch_chained(lru_scan_kernel<float>, grid, kLruChannels, kLruScanSmem, stream, (const float*)gates, y, (float*)out, state,
+        launch_chained(lru_scan_kernel<float>, grid, kLruScanThreads, kLruScanSmem, stream, (const float*)gates, y, (float*)out, state,
                        slot_stride, span_begin, span_slot, width, vector_copies);
     else
-        launch_chained(lru_scan_kernel<__nv_bfloat16>, grid, kLruChannels, kLruScanSmem, stream, (const float*)gates, y,
+        launch_chained(lru_scan_kernel<__nv_bfloat16>, grid, kLruScanThreads, kLruScanSmem, stream, (const float*)gates, y,
                        (__nv_bfloat16*)out, state, slot_stride, span_begin, span_slot, width, vector_copies);
     return check_launch("lru_scan");
 }
