@@ -641,3 +641,96 @@ def test_configurations_drawn_at_random(tmp_path, seed):
         else:
             for rows, target in ((whole, want["a"]), (got["a"], want["a"]), (got["b"], want["b"])):
                 assert np.median(spread_error(np.asarray(rows, dtype=np.float64), target)) < 0.1
+
+
+# ------------------------------------------------------------------------------------------ trace replay
+def replay_steps(requests, seed):
+    """A schedule for up to four live requests: portions of changing size (two tokens too) beside single tokens,
+    requests left out of steps, ended requests followed by new ones. Returns (steps, {request: wanted places})."""
+    rng = np.random.default_rng(seed)
+    waiting = list(requests)
+    live, at, steps = [], {}, []
+    while waiting or live:
+        while waiting and len(live) < 4:
+            name = waiting.pop(0)
+            live.append(name)
+            at[name] = 0
+        entries, ended = [], []
+        for name in list(live):
+            tokens = requests[name]
+            left = len(tokens) - at[name]
+            if len(live) > 1 and rng.random() < 0.2:
+                continue                                       # (left out of this step)
+            count = min(left, int(rng.choice([1, 1, 2, 3, 17, 40])))
+            entries.append({"id": name, "tokens": tokens[at[name]:at[name] + count], "want": list(range(count))})
+            at[name] += count
+            if at[name] == len(tokens):
+                ended.append(name)
+                live.remove(name)
+        if entries:
+            steps.append({"step": len(steps), "entries": entries, "end": ended})
+    return steps
+
+
+LIGHTNING_ONLY = nm.config(70, 40, [nm.with_mlp(nm.lightning(2, 8, 12, [0.9, 1.0]), nm.dense(24)),
+                                    nm.with_mlp(nm.lightning(1, 20, 4), None)])
+PARALLEL_ONLY = nm.config(90, 24, [nm.with_mlp(nm.parallel(2, 2, 8, 4, 9, 16, 2, 3), None),
+                                   nm.with_mlp(nm.parallel(4, 1, 4, 8, None, 8, 1, 2, scale=0.4), nm.moe(3, 2, 8))])
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["mixed", "odd", "lightning_only", "parallel_only"])
+def test_replay_with_pages_and_slots_used_again(models, name, dtype, tmp_path):
+    """Seven requests (640 positions in whole blocks of 64) through the trace runner's step loop with a pool for 448
+    positions, what four live ones can hold at most, and four slots."""
+    import io
+    import json
+    import os
+    from celeg_b200.engine.trace import replay
+    if name in models:
+        folder, raw, tensors = models[name]
+    else:
+        folder = str(tmp_path / name)
+        raw, bf16 = nm.write_model(folder, LIGHTNING_ONLY if name == "lightning_only" else PARALLEL_ONLY, 77)
+        tensors = plain.as_float64(bf16)
+    lengths = [70, 9, 100, 33, 64, 2, 81]
+    requests = {f"r{i}": tokens_of(raw["vocab"], n, 300 + i) for i, n in enumerate(lengths)}
+    steps = replay_steps(requests, 5)
+    out_dir = str(tmp_path / f"out_{dtype}")
+    done = io.StringIO()
+    text = io.StringIO("".join(json.dumps(step) + "\n" for step in steps))
+    assert replay(folder, dtype, out_dir, 448, text, done, max_requests=4) == 0
+    assert done.getvalue().split() == [w for step in steps for w in ("done", str(step["step"]))]
+    rows = {key: [] for key in requests}
+    for step in steps:
+        data = np.fromfile(os.path.join(out_dir, f"{step['step']}.f32"), dtype="<f4").reshape(-1, raw["vocab"])
+        row = 0
+        for entry in step["entries"]:
+            rows[entry["id"]].append(data[row:row + len(entry["want"])])
+            row += len(entry["want"])
+        assert row == data.shape[0]
+    for key, tokens in requests.items():
+        check(np.concatenate(rows[key]), plain.logits(raw, tensors, tokens), dtype, f"{name} request {key} replayed", routed=True)
+
+
+def test_the_trace_runner_as_a_program(models, tmp_path):
+    import json
+    import os
+    import subprocess
+    import sys
+    folder, raw, tensors = models["odd"]
+    tokens = tokens_of(raw["vocab"], 21, 400)
+    steps = [{"step": 0, "entries": [{"id": "a", "tokens": tokens[:18], "want": [0, 17]}], "end": []},
+             {"step": 1, "entries": [{"id": "a", "tokens": tokens[18:20], "want": []}], "end": []},
+             {"step": 2, "entries": [{"id": "a", "tokens": tokens[20:], "want": [0]}], "end": ["a"]}]
+    program = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "bin", "trace_run")
+    out_dir = str(tmp_path / "out")
+    result = subprocess.run([program, "--model", folder, "--dtype", "float32", "--out", out_dir, "--max-tokens", "64"],
+                            input="".join(json.dumps(step) + "\n" for step in steps), capture_output=True, text=True,
+                            timeout=600, env=dict(os.environ, PYTHON=sys.executable))
+    assert result.returncode == 0, result.stderr[-2000:]
+    assert [line for line in result.stdout.split("\n") if line.startswith("done")] == ["done 0", "done 1", "done 2"]
+    assert not os.path.exists(os.path.join(out_dir, "1.f32"))
+    want = plain.logits(raw, tensors, tokens)
+    got = np.concatenate([np.fromfile(os.path.join(out_dir, f"{n}.f32"), dtype="<f4").reshape(-1, raw["vocab"]) for n in (0, 2)])
+    check(got, want[[0, 17, 20]], "float32", "the program's logits")
