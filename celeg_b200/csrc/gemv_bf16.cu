@@ -34,6 +34,7 @@ constexpr int kGemvMaxConvTaps = 16;
 
 enum GemvMode : int { kGemvStoreBf16 = 0, kGemvStoreF32 = 1, kGemvAddResidual = 2, kGemvSwiGlu = 3, kGemvConv = 4,
                       kGemvActivation = 5 };     // y bfloat16 = act(x w^T); which activation travels in the `taps` argument
+// (kGemvSwiglu: `taps` = 1 + a code of activate() names another function of the gate than SiLU; 0: SiLU)
 
 struct GemvConvArgs {
     const float* conv_w;         // [channels, taps]
@@ -361,7 +362,7 @@ gemv_bf16_kernel(const __nv_bfloat16* x, int ldx, const __nv_bfloat16* __restric
             const float gate = __bfloat162float(__float2bfloat16_rn(sum[0]));
             const float up = __bfloat162float(__float2bfloat16_rn(sum[WT - 1]));
             reinterpret_cast<__nv_bfloat16*>(y)[(size_t)out_row * ldy + out_col] =
-                __float2bfloat16_rn(gate / (1.0f + expf(-gate)) * up);
+                __float2bfloat16_rn((conv.taps > 0 ? activate(gate, conv.taps - 1) : gate / (1.0f + expf(-gate))) * up);
         }
     }
     if (MODE == kGemvAddResidual && norm.next_w) {

@@ -468,7 +468,8 @@ def gemv_bf16(x, w: torch.Tensor, y: torch.Tensor, rows: int, mode: int = GEMV_S
               ahead: Optional[Tuple[int, int]] = None) -> None:
     """y[:rows] = x[:rows] @ w.T for at most 16 rows, streaming w once. mode GEMV_STORE: y bfloat16;
     GEMV_STORE_F32: y float32; GEMV_ADD_RESIDUAL: y float32, accumulated; GEMV_SWIGLU: w is
-    [2*inner, k] (gate rows, then up rows) and y bfloat16 [rows, inner] = silu(gate) * up; GEMV_CONV: w is
+    [2*inner, k] (gate rows, then up rows) and y bfloat16 [rows, inner] = silu(gate) * up (``taps`` = 1 + ACT_*:
+    that function of the gate instead); GEMV_CONV: w is
     [3*channels, k] (B, C, X rows of the short convolution's input projection), y bfloat16
     [rows, channels] = C * conv(B*X) over each request's carried state, which is shifted; row i is the
     single token of request i, whose state slot is span_slot[i]. GEMV_ACTIVATION: y bfloat16 = act(x w^T) with

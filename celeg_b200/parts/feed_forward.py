@@ -24,7 +24,8 @@ class SwiGluFeedForward:
     """down(silu(gate(x)) * up(x)); gate and up are one fused projection [2I, H] (gate rows
     first), as celeg concatenates w1 and w3 (src/backend/cpu/weights_loader.cpp:93-99;
     src/backend/cuda/packed/operators.cu:531-596). ``activation`` names another function of the gate (a gated
-    linear unit with ReLU, a GELU, ...); those run as the product and an element-wise kernel."""
+    linear unit with ReLU, a GELU, ...): in the weight-streaming product's epilogue for steps of few rows, else as the
+    product and an element-wise kernel."""
 
     def __init__(self, params: Mapping, weights: Mapping[str, torch.Tensor], parts: Mapping, rt: Runtime):
         self.rt = rt
@@ -46,11 +47,7 @@ class SwiGluFeedForward:
 
     def forward(self, x: torch.Tensor, out: torch.Tensor, step: StepContext) -> None:
         rt, t = self.rt, step.tokens
-        if self.activation == kernels.ACT_SILU:
-            rt.linear_swiglu(x, self.w_gate_up, self.gate_up, self.activated, t, self.inner)
-        else:
-            rt.linear(x, self.w_gate_up, self.gate_up, t)
-            kernels.glu(self.gate_up, self.activated, t, self.inner, self.activation)
+        rt.linear_swiglu(x, self.w_gate_up, self.gate_up, self.activated, t, self.inner, self.activation)
         rt.linear(self.activated, self.w_down, out, t)
 
 

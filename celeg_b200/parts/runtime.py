@@ -295,15 +295,21 @@ class Runtime:
                 torch.mm(x[:padded], weight.t(), out=out[:padded])
 
     def linear_swiglu(self, x: torch.Tensor, gate_up_weight: torch.Tensor, scratch: torch.Tensor,
-                      out: torch.Tensor, rows: int, inner: int) -> None:
-        """out[:rows] = silu(x gate^T) * (x up^T) with gate_up_weight = [gate rows; up rows]. Few
-        bfloat16 rows: one weight-streaming kernel; very many bfloat16 rows: one tcgen05 kernel; otherwise the
-        product into ``scratch`` and the activation kernel."""
+                      out: torch.Tensor, rows: int, inner: int, kind: int = kernels.ACT_SILU) -> None:
+        """out[:rows] = act(x gate^T) * (x up^T) with gate_up_weight = [gate rows; up rows], act = SiLU or the
+        ``kind`` given (a code of kernels.ACT_*). Few bfloat16 rows: one weight-streaming kernel; very many
+        bfloat16 rows and SiLU: one tcgen05 kernel; otherwise the product into ``scratch`` and the element-wise
+        kernel."""
         if rows == 0:
             return
         operand = x.xw if isinstance(x, kernels.SplitNorm) else x
         if self.act_dtype == torch.bfloat16 and kernels.gemv_supported(rows, operand, gate_up_weight):
-            kernels.gemv_bf16(x, gate_up_weight, out, rows, kernels.GEMV_SWIGLU, ahead=self._ahead(gate_up_weight))
+            kernels.gemv_bf16(x, gate_up_weight, out, rows, kernels.GEMV_SWIGLU, ahead=self._ahead(gate_up_weight),
+                              taps=0 if kind == kernels.ACT_SILU else 1 + kind)
+            return
+        if kind != kernels.ACT_SILU:
+            self.linear(x, gate_up_weight, scratch, rows)
+            kernels.glu(scratch, out, rows, inner, kind)
             return
         if (self.act_dtype == torch.bfloat16 and kernels.gemm_tcgen05_supported(x, gate_up_weight)
                 and (self.tensor_core_products == "all"

@@ -328,3 +328,21 @@ def test_router_bias_enters_the_choice_and_the_weights():
             assert set(got[t]) == set(order[t]), f"token {t}: chose {got[t]}, wanted {order[t]}"
             by_expert = dict(zip(order[t], weights[t]))
             assert all(abs(got_w[t, j] - by_expert[got[t, j]]) <= 2e-6 for j in range(top))
+
+
+def test_weight_streaming_gated_product_with_another_gate_function():
+    """Few rows: [gate | up] product and the gate's function in one launch; ReLU and the tanh GELU beside SiLU."""
+    k = kernels()
+    rng = np.random.default_rng(13)
+    for rows, width, inner in ((1, 64, 48), (8, 256, 352), (16, 128, 136)):
+        x = gpu(rng.normal(size=(rows, width)), torch.bfloat16)
+        w = gpu(rng.normal(size=(2 * inner, width)) / math.sqrt(width), torch.bfloat16)
+        assert k.gemv_supported(rows, x, w)
+        sums = x.double().cpu().numpy() @ w.double().cpu().numpy().T
+        sums = torch.as_tensor(sums).to(torch.bfloat16).double().numpy()          # both halves are rounded as if stored
+        gate, up = sums[:, :inner], sums[:, inner:]
+        for kind, function in ((k.ACT_SILU, lambda z: z * sigmoid(z)), (k.ACT_RELU, lambda z: np.maximum(z, 0.0)),
+                               (k.ACT_GELU_TANH, gelu_tanh)):
+            out = torch.zeros((rows, inner), dtype=torch.bfloat16, device=DEVICE)
+            k.gemv_bf16(x, w, out, rows, k.GEMV_SWIGLU, taps=0 if kind == k.ACT_SILU else 1 + kind)
+            close(out, function(gate) * up, 1.2e-2, f"gate function {kind} at {rows}x{width}x{inner}")
