@@ -734,3 +734,35 @@ def test_the_trace_runner_as_a_program(models, tmp_path):
     want = plain.logits(raw, tensors, tokens)
     got = np.concatenate([np.fromfile(os.path.join(out_dir, f"{n}.f32"), dtype="<f4").reshape(-1, raw["vocab"]) for n in (0, 2)])
     check(got, want[[0, 17, 20]], "float32", "the program's logits")
+
+
+# ------------------------------------------------------------------------------- layers of a real model's size
+@pytest.fixture(scope="module")
+def large(tmp_path_factory):
+    """Three layers 1,024 wide: lightning heads of 64 keys and 128 values with 32 gated experts and a shared one; eight
+    attention heads of 128 on two key heads under chunks of 256 beside a recurrent unit of 1,024 channels in blocks of
+    128 behind four taps, with a ReLU-gated feed-forward; lightning again. The sizes at which the grouped tensor-core
+    product, the segmented scan, the tensor-core attention kernels and the wide row norm are the ones that run."""
+    decay = [1.0 - 2.0 ** (-3 - head) for head in range(8)]
+    raw = nm.config(8192, 1024, [
+        nm.with_mlp(nm.lightning(8, 64, 128, decay), nm.moe(32, 4, 512, shared=1024)),
+        nm.with_mlp(nm.parallel(8, 2, 128, 128, 256, 1024, 8, 4, left_scale=1.1, right_scale=0.8), nm.dense(2816)),
+        nm.with_mlp(nm.lightning(8, 64, 128, decay), nm.dense(1536)),
+    ])
+    folder = str(tmp_path_factory.mktemp("naselorn_large") / "model")
+    raw, bf16 = nm.write_model(folder, raw, 91)
+    tensors = plain.as_float64(bf16)
+    first, second = tokens_of(raw["vocab"], 608, 500), tokens_of(raw["vocab"], 450, 501)
+    return folder, raw, {"a": first, "b": second}, {"a": plain.logits(raw, tensors, first), "b": plain.logits(raw, tensors, second)}
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_layers_of_a_real_model_size(large, dtype):
+    folder, raw, requests, want = large
+    first, second = requests["a"], requests["b"]
+    loaded = load(folder, dtype, cache_tokens=2048, max_batched_tokens=1024, max_context=1024)
+    steps = [[("a", first[:600])], [("a", first[600:601]), ("b", second[:300])], [("a", first[601:602]), ("b", second[300:])]]
+    steps += [[("a", [t])] for t in first[602:]]
+    got = run_steps(loaded, steps)
+    for key in ("a", "b"):
+        check(got[key], want[key], dtype, f"request {key} at a real model's layer sizes", routed=True)
