@@ -15,6 +15,9 @@ from .kedesun_arch import build_kedesun_spec
 from .naselorn import NaselornConfig
 from . import naselorn_arch as _naselorn_arch  # registers "Naselorn"
 from .naselorn_arch import build_naselorn_spec
+from .liverax import LiveraxConfig
+from . import liverax_arch as _liverax_arch  # registers "Liverax"
+from .liverax_arch import build_liverax_spec
 
 __all__ = [
     "Architecture", "ConfigError", "UnknownArchitectureError", "ExecutionEntry", "LayerSpec",
@@ -22,4 +25,5 @@ __all__ = [
     "known_architectures", "read_config_json", "register_architecture", "CONV",
     "FULL_ATTENTION", "Lfm2Config", "build_lfm2_spec", "RamosunConfig", "build_ramosun_spec",
     "KedesunConfig", "build_kedesun_spec", "NaselornConfig", "build_naselorn_spec",
+    "LiveraxConfig", "build_liverax_spec",
 ]

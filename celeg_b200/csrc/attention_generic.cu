@@ -7,6 +7,9 @@
 // Values may have another size than keys (``value_dim``), and instead of a window of recent positions a query may be
 // limited to the keys of its own chunk of ``chunk`` positions, chunks counted from position 0 of the sequence.
 //
+// An optional table per query head of numbers by distance (query position minus key position, the last entry for
+// everything farther) is added to the scaled scores.
+//
 // An optional sink per query head (a learned score that enters the denominator once, unscaled, with no
 // value) is where the running maximum and denominator start.
 //
@@ -30,6 +33,7 @@ __global__ void attention_generic_kernel(const A* __restrict__ q, int q_row_stri
                                          const int* __restrict__ block_table, int table_stride, int tokens,
                                          int q_heads, int kv_heads, int head_dim, int value_dim, int page_tokens,
                                          int window, int chunk, float scale, const float* __restrict__ sinks,
+                                         const float* __restrict__ distance_bias, int distance_last,
                                          int* __restrict__ error_flag) {
     extern __shared__ float q_smem[];
     const int warp = threadIdx.x >> 5;
@@ -70,6 +74,8 @@ __global__ void attention_generic_kernel(const A* __restrict__ q, int q_row_stri
                 const A* kv = k_cache + (long long)page * page_stride + place * head_dim;
                 float s = 0.0f;
                 for (int i = 0; i < head_dim; ++i) s += qs[i] * to_float(kv[i]);
+                // a learned number per (head, distance back to the key), added to the scaled score as it is
+                if (distance_bias) s += distance_bias[(size_t)h * (distance_last + 1) + min(pos - key, distance_last)];
                 score = s;
             }
         }
@@ -109,13 +115,15 @@ using namespace celeg_b200;
 
 // q: [tokens, q_row_stride] with head h at columns h*head_dim; out: [tokens, q_heads*value_dim]. value_dim 0: as wide
 // as the keys. chunk > 0: a query reads the keys of its own chunk of that many positions (and no window).
+// distance_bias: float32 [q_heads, distance_last + 1] or null; entry [h, min(n, distance_last)] is added to the scaled
+// score of head h for a key n positions back.
 CELEG_API int celeg_attention_generic(const void* q, int q_row_stride, void* out, const void* k_cache,
                                       const void* v_cache, long long page_stride, long long value_page_stride,
                                       int value_dim, int chunk, const int* positions,
                                       const int* token_span, const int* block_table, int table_stride,
                                       int tokens, int q_heads, int kv_heads, int head_dim, int page_tokens,
-                                      int window, float scale, const float* sinks, int* error_flag, int act_dtype,
-                                      cudaStream_t stream) {
+                                      int window, float scale, const float* sinks, const float* distance_bias,
+                                      int distance_last, int* error_flag, int act_dtype, cudaStream_t stream) {
     CELEG_REQUIRE(tokens >= 0 && q_heads > 0 && kv_heads > 0 && head_dim > 0 && page_tokens > 0,
                   "attention: invalid sizes tokens=%d q_heads=%d kv_heads=%d head_dim=%d page_tokens=%d", tokens,
                   q_heads, kv_heads, head_dim, page_tokens);
@@ -136,13 +144,13 @@ CELEG_API int celeg_attention_generic(const void* q, int q_row_stride, void* out
         attention_generic_kernel<float><<<blocks, warps * 32, smem, stream>>>(
             (const float*)q, q_row_stride, (float*)out, (const float*)k_cache, (const float*)v_cache, page_stride,
             value_page_stride, positions, token_span, block_table, table_stride, tokens, q_heads, kv_heads, head_dim,
-            value_dim, page_tokens, window, chunk, scale, sinks, error_flag);
+            value_dim, page_tokens, window, chunk, scale, sinks, distance_bias, distance_last, error_flag);
     else if (act_dtype == kBFloat16)
         attention_generic_kernel<__nv_bfloat16><<<blocks, warps * 32, smem, stream>>>(
             (const __nv_bfloat16*)q, q_row_stride, (__nv_bfloat16*)out, (const __nv_bfloat16*)k_cache,
             (const __nv_bfloat16*)v_cache, page_stride, value_page_stride, positions, token_span, block_table,
             table_stride, tokens, q_heads, kv_heads, head_dim, value_dim, page_tokens, window, chunk, scale, sinks,
-            error_flag);
+            distance_bias, distance_last, error_flag);
     else
         CELEG_REQUIRE(false, "attention: unknown dtype code %d", act_dtype);
     return check_launch("attention_generic");

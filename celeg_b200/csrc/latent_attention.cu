@@ -11,11 +11,12 @@
 //   latent_prepare   c = rms_norm(down[:rank]) * w -> cache;  r = rotate(down[rank:]) -> cache;
 //                    rotate(q_h[dim:]) -> absorbed query [.., rank:]
 //   head_project     out[t, h, :] = in[t, h, :] . M_h for a matrix per head taken out of a stored [out, in]
-//                    projection (either orientation), optionally times sigmoid(gate[t, h]):
+//                    projection (either orientation), optionally times sigmoid(gate[t, h]) or, with a gate per
+//                    output element, sigmoid(gate[t, h, n]):
 //                    the absorption (U_h^T q_h) and the value up-projection with the head's output gate
 //
-// Rotation: dimensions (2i, 2i + 1) form a pair, angle = position x frequency_i (frequencies come scaled from the
-// host), cos and sin times `magnitude`. Sums, norms and angles are float32; cache and query have the activation type.
+// Rotation: dimensions (2i, 2i + 1) form a pair (or, where asked for, i and i + half of the rotated dimensions),
+// angle = position x frequency_i (frequencies come scaled from the host), cos and sin times `magnitude`. Sums, norms and angles are float32; cache and query have the activation type.
 #include "common.cuh"
 
 namespace celeg_b200 {
@@ -30,6 +31,7 @@ struct LatentPrepareArgs {
     void* cache; long long page_stride; int page_tokens;     // pages of [page_tokens, rank + rot]
     void* query; int query_stride;            // [tokens, heads * (rank + rot)]: the rotated part is written here
     int heads, dim, rot, rotated, rank;      // rot: width of the rotated part; rotated <= rot: how much of it turns
+    int halves;                               // pairs are (i, i + rotated / 2) instead of neighbours (2i, 2i + 1)
     int* error_flag;
 };
 
@@ -64,9 +66,10 @@ __global__ void latent_prepare_kernel(const LatentPrepareArgs a) {
         for (int i = threadIdx.x; i < a.rank; i += blockDim.x)
             dst[i] = from_float<A>(to_float(down[i]) * inv * a.norm_weight[i]);
         for (int i = threadIdx.x; i < half; i += blockDim.x) {
-            const float u = to_float(down[a.rank + 2 * i]), v = to_float(down[a.rank + 2 * i + 1]);
-            dst[a.rank + 2 * i] = from_float<A>(u * turn[i] - v * turn[half + i]);
-            dst[a.rank + 2 * i + 1] = from_float<A>(v * turn[i] + u * turn[half + i]);
+            const int first = a.halves ? i : 2 * i, second = a.halves ? i + half : 2 * i + 1;
+            const float u = to_float(down[a.rank + first]), v = to_float(down[a.rank + second]);
+            dst[a.rank + first] = from_float<A>(u * turn[i] - v * turn[half + i]);
+            dst[a.rank + second] = from_float<A>(v * turn[i] + u * turn[half + i]);
         }
         for (int i = a.rotated + threadIdx.x; i < a.rot; i += blockDim.x) dst[a.rank + i] = down[a.rank + i];
     }
@@ -76,9 +79,10 @@ __global__ void latent_prepare_kernel(const LatentPrepareArgs a) {
         const int h = unit / half, i = unit - h * half;
         const A* src = q + (size_t)h * (a.dim + a.rot) + a.dim;
         A* dst = query + (size_t)h * (a.rank + a.rot) + a.rank;
-        const float u = to_float(src[2 * i]), v = to_float(src[2 * i + 1]);
-        dst[2 * i] = from_float<A>(u * turn[i] - v * turn[half + i]);
-        dst[2 * i + 1] = from_float<A>(v * turn[i] + u * turn[half + i]);
+        const int first = a.halves ? i : 2 * i, second = a.halves ? i + half : 2 * i + 1;
+        const float u = to_float(src[first]), v = to_float(src[second]);
+        dst[first] = from_float<A>(u * turn[i] - v * turn[half + i]);
+        dst[second] = from_float<A>(v * turn[i] + u * turn[half + i]);
     }
     const int rest = a.rot - a.rotated;
     for (int unit = threadIdx.x; unit < a.heads * rest; unit += blockDim.x) {
@@ -94,7 +98,8 @@ struct HeadProjectArgs {
     const void* in; int in_stride, in_head;
     const void* matrix; long long m_head, m_k, m_n;
     void* out; int out_stride, out_head;
-    const void* gate; int gate_stride;        // activation type [tokens, heads] or null
+    const void* gate; int gate_stride;        // activation type [tokens, heads * gate_width] or null
+    int gate_width;                           // 1: a gate per head; n: a gate per output element
     int tokens, n, k;
 };
 
@@ -145,12 +150,16 @@ __global__ void __launch_bounds__(256) head_project_kernel(const HeadProjectArgs
     for (int i = 0; i < 4; ++i) {
         const int gr = row0 + ty * 4 + i;
         if (gr >= a.tokens) continue;
+        const A* gate = a.gate ? static_cast<const A*>(a.gate) + (size_t)gr * a.gate_stride + (size_t)head * a.gate_width
+                               : nullptr;
         float factor = 1.0f;
-        if (a.gate) factor = 1.0f / (1.0f + expf(-to_float(static_cast<const A*>(a.gate)[(size_t)gr * a.gate_stride + head])));
+        if (gate && a.gate_width == 1) factor = 1.0f / (1.0f + expf(-to_float(gate[0])));
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
             const int gc = col0 + tx * 4 + j;
-            if (gc < a.n) out[(size_t)gr * a.out_stride + gc] = from_float<A>(acc[i][j] * factor);
+            if (gc >= a.n) continue;
+            if (gate && a.gate_width > 1) factor = 1.0f / (1.0f + expf(-to_float(gate[gc])));
+            out[(size_t)gr * a.out_stride + gc] = from_float<A>(acc[i][j] * factor);
         }
     }
 }
@@ -178,8 +187,8 @@ CELEG_API int celeg_latent_prepare(const void* q, int q_stride, const void* down
                                    const float* norm_weight, const float* frequencies, float magnitude, float eps,
                                    const int* positions, const int* token_span, const int* block_table,
                                    int table_stride, void* cache, long long page_stride, int page_tokens, void* query,
-                                   int query_stride, int tokens, int heads, int dim, int rot, int rotated, int rank, int* error_flag,
-                                   int act_dtype, cudaStream_t stream) {
+                                   int query_stride, int tokens, int heads, int dim, int rot, int rotated, int rank, int halves,
+                                   int* error_flag, int act_dtype, cudaStream_t stream) {
     CELEG_REQUIRE(tokens >= 0 && heads > 0 && dim >= 0 && rot >= 0 && rotated >= 0 && rotated <= rot && rotated % 2 == 0 &&
                   rank > 0 && page_tokens > 0 && eps > 0.0f,
                   "latent_prepare: invalid sizes tokens=%d heads=%d dim=%d rot=%d rotated=%d rank=%d page_tokens=%d",
@@ -189,7 +198,7 @@ CELEG_API int celeg_latent_prepare(const void* q, int q_stride, const void* down
     if (tokens == 0) return 0;
     const LatentPrepareArgs args = {q, q_stride, down, down_stride, norm_weight, frequencies, magnitude, eps, positions,
                                     token_span, block_table, table_stride, cache, page_stride, page_tokens, query,
-                                    query_stride, heads, dim, rot, rotated, rank, error_flag};
+                                    query_stride, heads, dim, rot, rotated, rank, halves, error_flag};
     const size_t smem = (size_t)(rotated + 2) * sizeof(float);
     if (act_dtype == kFloat32)
         launch_chained(latent_prepare_kernel<float>, tokens, 128, smem, stream, args);
@@ -200,17 +209,19 @@ CELEG_API int celeg_latent_prepare(const void* q, int q_stride, const void* down
 
 CELEG_API int celeg_head_project(const void* in, int in_stride, int in_head, const void* matrix, long long m_head,
                                  long long m_k, long long m_n, void* out, int out_stride, int out_head, const void* gate,
-                                 int gate_stride, int tokens, int heads, int n, int k, int act_dtype,
+                                 int gate_stride, int gate_width, int tokens, int heads, int n, int k, int act_dtype,
                                  cudaStream_t stream) {
     CELEG_REQUIRE(tokens >= 0 && heads > 0 && n > 0 && k > 0 && (m_k == 1 || m_n == 1),
                   "head_project: invalid sizes tokens=%d heads=%d n=%d k=%d m_k=%lld m_n=%lld", tokens, heads, n, k, m_k,
                   m_n);
+    CELEG_REQUIRE(!gate || gate_width == 1 || gate_width == n, "head_project: a gate of %d numbers for a head of %d outputs",
+                  gate_width, n);
     CELEG_REQUIRE(heads <= 65535 && (tokens + 63) / 64 <= 65535, "head_project: %d heads or %d tokens exceed one launch",
                   heads, tokens);
     CELEG_REQUIRE(act_dtype == kFloat32 || act_dtype == kBFloat16, "head_project: unknown dtype code %d", act_dtype);
     if (tokens == 0) return 0;
     const HeadProjectArgs args = {in, in_stride, in_head, matrix, m_head, m_k, m_n, out, out_stride, out_head, gate,
-                                  gate_stride, tokens, n, k};
+                                  gate_stride, gate_width, tokens, n, k};
     dim3 grid((n + 63) / 64, (tokens + 63) / 64, heads);
     if (act_dtype == kFloat32)
         launch_chained(head_project_kernel<float>, grid, 256, 0, stream, args);

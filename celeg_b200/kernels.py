@@ -46,7 +46,16 @@ _SIGNATURES = {
                                  c_int, c_void_p, c_int, c_void_p],
     "celeg_attention_generic": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_longlong, c_longlong, c_int, c_int,
                                 c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float,
-                                c_void_p, c_void_p, c_int, c_void_p],
+                                c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p],
+    "celeg_qkv_prepare": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_float, c_void_p, c_int, c_float, c_int, c_int,
+                          c_float, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
+                          c_void_p, c_longlong, c_longlong, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
+                          c_void_p, c_int, c_void_p],
+    "celeg_add_layernorm": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_float, c_int,
+                            c_int, c_void_p],
+    "celeg_rmsnorm_strided": [c_void_p, c_longlong, c_void_p, c_void_p, c_longlong, c_int, c_int, c_float, c_int,
+                              c_void_p],
+    "celeg_sigmoid_gate": [c_void_p, c_longlong, c_void_p, c_longlong, c_int, c_int, c_int, c_int, c_void_p],
     "celeg_bias_store_kv": [c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
                             c_void_p, c_longlong, c_longlong, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
                             c_void_p, c_int, c_void_p],
@@ -127,9 +136,9 @@ _SIGNATURES = {
                             c_float, c_int, c_int, c_int, c_void_p],
     "celeg_latent_prepare": [c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_float, c_float, c_void_p, c_void_p,
                              c_void_p, c_int, c_void_p, c_longlong, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int,
-                             c_int, c_int, c_void_p, c_int, c_void_p],
+                             c_int, c_int, c_int, c_void_p, c_int, c_void_p],
     "celeg_head_project": [c_void_p, c_int, c_int, c_void_p, c_longlong, c_longlong, c_longlong, c_void_p, c_int, c_int,
-                           c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
+                           c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
     "celeg_head_gate": [c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
     "celeg_moe_route": [c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
     "celeg_moe_group": [c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p],
@@ -318,18 +327,90 @@ def attention_generic(q: torch.Tensor, q_row_stride: int, out: torch.Tensor, k_c
                       block_table: torch.Tensor, tokens: int, q_heads: int, kv_heads: int, head_dim: int,
                       page_tokens: int, window: Optional[int], scale: float, error_flag: torch.Tensor,
                       sinks: Optional[torch.Tensor] = None, value_dim: Optional[int] = None,
-                      chunk: Optional[int] = None) -> None:
+                      chunk: Optional[int] = None, distance_bias: Optional[torch.Tensor] = None) -> None:
     """``sinks``: float32 [q_heads] or None; a head's sink is a score that enters the denominator of each of its
     rows once, unscaled, without key or value. ``value_dim``: the values' size when it is not the keys' (``out`` is
     then [tokens, q_heads * value_dim]). ``chunk``: a query reads only the keys of its own chunk of that many
-    positions, counted from position 0 (no window then)."""
+    positions, counted from position 0 (no window then). ``distance_bias``: float32 [q_heads, n + 1] or None; entry
+    [h, min(distance, n)] is added to head h's scaled score of a key ``distance`` positions back."""
     if sinks is not None:
         _need(sinks, torch.float32, "sinks")
+    bias_ptr, bias_last = _distance_bias(distance_bias, q_heads)
     _check(library().celeg_attention_generic(
         _ptr(q), q_row_stride, _ptr(out), _ptr(k_cache), _ptr(v_cache), k_cache.stride(0), v_cache.stride(0),
         int(value_dim or 0), int(chunk or 0), _ptr(positions),
         _ptr(token_span), _ptr(block_table), block_table.stride(0), tokens, q_heads, kv_heads, head_dim,
-        page_tokens, int(window or 0), scale, _ptr(sinks), _ptr(error_flag), dtype_code(q.dtype), _stream()))
+        page_tokens, int(window or 0), scale, _ptr(sinks), bias_ptr, bias_last, _ptr(error_flag), dtype_code(q.dtype),
+        _stream()))
+
+
+def _distance_bias(table: Optional[torch.Tensor], q_heads: int) -> Tuple[Optional[int], int]:
+    """(address, last column) of a table of score biases by distance, [q_heads, last + 1] float32, or (None, 0)."""
+    if table is None:
+        return None, 0
+    _need(table, torch.float32, "distance_bias")
+    assert table.dim() == 2 and table.shape[0] == q_heads and table.is_contiguous() and table.shape[1] >= 1
+    return _ptr(table), int(table.shape[1]) - 1
+
+
+def qkv_prepare(proj: torch.Tensor, bias: Optional[torch.Tensor], q_out: torch.Tensor, positions: torch.Tensor,
+                token_span: torch.Tensor, block_table: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
+                tokens: int, q_heads: int, kv_heads: int, head_dim: int, value_dim: int, key_store: int,
+                value_store: int, page_tokens: int, error_flag: torch.Tensor, *,
+                q_norm: Optional[torch.Tensor] = None, k_norm: Optional[torch.Tensor] = None, norm_eps: float = 0.0,
+                frequencies: Optional[torch.Tensor] = None, rotary_dim: int = 0,
+                temperature: Optional[Tuple[float, int]] = None, blend: int = 0, lam: float = 0.0,
+                first_values: Optional[torch.Tensor] = None) -> None:
+    """Float32 rows [q heads | k heads | v heads | ...] as projected become queries in ``q_out`` and keys and values
+    in the tokens' places of the paged cache (csrc/attention_prepare.cu), after, in this order: the biases; one RMS
+    norm over the whole q projection and one over the whole k projection (``q_norm`` / ``k_norm``, as wide as the
+    projections); the rotation of the first ``rotary_dim`` entries of every q and k head in pairs (i, i + half) by
+    position x ``frequencies``; ``temperature`` = (coef, every): q times 1 + coef ln(floor((position + 1) / every) + 1);
+    ``blend`` 1: the values are noted in ``first_values`` (float32 [tokens, kv_heads * value_dim]); 2: v becomes
+    (1 - lam) v + lam first_values. One rounding."""
+    _need(proj, torch.float32, "proj")
+    for vector in (bias, q_norm, k_norm, frequencies, first_values):
+        if vector is not None:
+            _need(vector, torch.float32, "a vector of qkv_prepare")
+    assert q_out.dtype == k_cache.dtype == v_cache.dtype and q_out.stride(-1) == 1 and proj.stride(-1) == 1
+    coef, every = temperature if temperature else (0.0, 0)
+    _check(library().celeg_qkv_prepare(
+        _ptr(proj), proj.stride(0), _ptr(bias), _ptr(q_norm), _ptr(k_norm), norm_eps, _ptr(frequencies), rotary_dim,
+        float(coef), int(every), blend, lam, _ptr(first_values), first_values.stride(0) if first_values is not None else 0,
+        _ptr(q_out), q_out.stride(0), _ptr(positions), _ptr(token_span), _ptr(block_table), block_table.stride(0),
+        _ptr(k_cache), _ptr(v_cache), k_cache.stride(0), v_cache.stride(0), tokens, q_heads, kv_heads, head_dim, value_dim,
+        key_store, value_store, page_tokens, _ptr(error_flag), dtype_code(q_out.dtype), _stream()))
+
+
+def add_layernorm(residual: torch.Tensor, delta: Optional[torch.Tensor], weight: torch.Tensor, out: torch.Tensor,
+                  eps: float, rows: Optional[torch.Tensor] = None, n_rows: Optional[int] = None,
+                  bias: Optional[torch.Tensor] = None) -> None:
+    """out[i] = (x - mean(x)) / sqrt(mean((x - mean(x))^2) + eps) * weight (+ bias) of x = residual[r] + delta[r];
+    residual[r] is updated when not gathering (csrc/layernorm.cu)."""
+    _need(residual, torch.float32, "residual")
+    _need(weight, torch.float32, "weight")
+    width = residual.shape[-1]
+    if n_rows is None:
+        n_rows = rows.shape[0] if rows is not None else residual.shape[0]
+    if delta is not None:
+        assert delta.dtype == out.dtype and delta.shape[-1] == width
+    _check(library().celeg_add_layernorm(_ptr(residual), _ptr(delta), _ptr(weight), _ptr(bias), _ptr(out), _ptr(rows),
+                                         n_rows, width, eps, int(rows is None), dtype_code(out.dtype), _stream()))
+
+
+def rmsnorm_strided(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, eps: float, n_rows: int) -> None:
+    """RMS norm of the rows of a 2-D view (a slice of a wider buffer's columns) into another."""
+    _need(weight, torch.float32, "weight")
+    assert x.dtype == out.dtype and x.stride(-1) == 1 and out.stride(-1) == 1 and x.shape[-1] == out.shape[-1]
+    _check(library().celeg_rmsnorm_strided(_ptr(x), x.stride(0), _ptr(weight), _ptr(out), out.stride(0), n_rows,
+                                           x.shape[-1], eps, dtype_code(x.dtype), _stream()))
+
+
+def sigmoid_gate(values: torch.Tensor, gate: torch.Tensor, tokens: int, width: int) -> None:
+    """values[t, c] *= sigmoid(gate[t, c]) for c < width, in place; ``gate`` float32 or of the values' type."""
+    assert values.stride(-1) == 1 and gate.stride(-1) == 1
+    _check(library().celeg_sigmoid_gate(_ptr(values), values.stride(0), _ptr(gate), gate.stride(0), tokens, width,
+                                        dtype_code(values.dtype), dtype_code(gate.dtype), _stream()))
 
 
 def bias_store_kv(proj: torch.Tensor, bias: Optional[torch.Tensor], q_out: torch.Tensor, positions: torch.Tensor,
@@ -864,25 +945,29 @@ def depth_average(stream: torch.Tensor, delta_a: Optional[torch.Tensor], delta_b
 def latent_prepare(q: torch.Tensor, down: torch.Tensor, norm_weight: torch.Tensor, frequencies: torch.Tensor,
                    magnitude: float, eps: float, positions: torch.Tensor, token_span: torch.Tensor,
                    block_table: torch.Tensor, cache: torch.Tensor, page_tokens: int, query: torch.Tensor, tokens: int,
-                   heads: int, dim: int, rot: int, rotated: int, rank: int, error_flag: torch.Tensor) -> None:
+                   heads: int, dim: int, rot: int, rotated: int, rank: int, error_flag: torch.Tensor,
+                   halves: bool = False) -> None:
     """The latent attention's token-parallel step (csrc/latent_attention.cu): the normalised latent vector and the
     rotated shared key part go to the token's place in ``cache`` (pages of [page_tokens, rank + rot]), every head's
     rotated query part to ``query[t, h, rank:]`` ([tokens, heads * (rank + rot)]). Of the ``rot`` dimensions of a
-    rotated part the first ``rotated`` turn (pairs of neighbours), the rest pass unchanged."""
+    rotated part the first ``rotated`` turn (pairs of neighbours, or with ``halves`` pairs (i, i + rotated / 2)), the
+    rest pass unchanged."""
     assert q.dtype == down.dtype == cache.dtype == query.dtype and q.stride(-1) == 1 and down.stride(-1) == 1
     assert query.stride(-1) == 1 and cache.is_contiguous()
     _check(library().celeg_latent_prepare(
         _ptr(q), q.stride(0), _ptr(down), down.stride(0), _ptr(norm_weight), _ptr(frequencies), magnitude, eps,
         _ptr(positions), _ptr(token_span), _ptr(block_table), block_table.stride(0), _ptr(cache), cache.stride(0),
-        page_tokens, _ptr(query), query.stride(0), tokens, heads, dim, rot, rotated, rank, _ptr(error_flag), dtype_code(q.dtype),
-        _stream()))
+        page_tokens, _ptr(query), query.stride(0), tokens, heads, dim, rot, rotated, rank, int(halves), _ptr(error_flag),
+        dtype_code(q.dtype), _stream()))
 
 
 def head_project(x: torch.Tensor, in_head: int, matrix: torch.Tensor, contract_rows: bool, out: torch.Tensor,
-                 out_head: int, tokens: int, heads: int, n: int, k: int, gate: Optional[torch.Tensor] = None) -> None:
+                 out_head: int, tokens: int, heads: int, n: int, k: int, gate: Optional[torch.Tensor] = None,
+                 gate_per_element: bool = False) -> None:
     """out[t, h * out_head + j] = sum_i x[t, h * in_head + i] M_h[i, j] (times sigmoid(gate[t, h])) for j < n, i < k.
     ``matrix`` is a stored projection [heads * rows, columns]: with ``contract_rows`` M_h[i, j] = matrix[h * k + i, j]
-    (the sum runs over the head's rows), else M_h[i, j] = matrix[h * n + j, i] (over its columns)."""
+    (the sum runs over the head's rows), else M_h[i, j] = matrix[h * n + j, i] (over its columns). With
+    ``gate_per_element`` the gate is [tokens, heads * n] and the factor sigmoid(gate[t, h * n + j])."""
     assert x.dtype == matrix.dtype == out.dtype and x.stride(-1) == 1 and out.stride(-1) == 1 and matrix.is_contiguous()
     columns = matrix.shape[1]
     if contract_rows:
@@ -893,7 +978,7 @@ def head_project(x: torch.Tensor, in_head: int, matrix: torch.Tensor, contract_r
         assert gate.dtype == x.dtype and gate.stride(-1) == 1
     _check(library().celeg_head_project(_ptr(x), x.stride(0), in_head, _ptr(matrix), m_head, m_k, m_n, _ptr(out),
                                         out.stride(0), out_head, _ptr(gate), gate.stride(0) if gate is not None else 0,
-                                        tokens, heads, n, k, dtype_code(x.dtype), _stream()))
+                                        n if gate_per_element else 1, tokens, heads, n, k, dtype_code(x.dtype), _stream()))
 
 
 def head_gate(values: torch.Tensor, head_width: int, gate: torch.Tensor, tokens: int, heads: int) -> None:

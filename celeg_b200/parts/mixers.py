@@ -17,6 +17,7 @@ in the StepContext, everything about its cache in the binding.
 """
 from __future__ import annotations
 
+import math
 from dataclasses import dataclass
 from typing import Mapping, Optional
 
@@ -151,7 +152,7 @@ class PagedAttentionKernels:
         among the query heads of a group and splits long contexts, where a prompt kernel would walk the whole
         context once per query head for one row of a 128-row tile."""
         rt = self.rt
-        if self._values_differ():
+        if self._values_differ() or getattr(self, "distance_bias", None) is not None:
             self._attend_general(step, table, 0)
             return
         if self._decodes(step):
@@ -214,7 +215,7 @@ class PagedAttentionKernels:
                                   step.positions[skip:], step.token_span[skip:], table, step.tokens - skip,
                                   self.heads, self.kv_heads, self.head_dim, b.page_tokens, self.window, self.scale,
                                   step.error_flag, sinks=self.sinks, value_dim=getattr(self, "value_dim", None),
-                                  chunk=getattr(self, "chunk", None))
+                                  chunk=getattr(self, "chunk", None), distance_bias=getattr(self, "distance_bias", None))
 
 
 @register_part("mixer", "attention")
@@ -340,19 +341,54 @@ class AttentionMixer(PagedAttentionKernels):
         rt.linear(self.attended, self.w_out, out, t)
 
 
-@register_part("mixer", "chunked_attention")
-class ChunkedAttentionMixer(PagedAttentionKernels):
-    """Causal grouped-query softmax attention without any position encoding, with optional biases on its four
-    projections (tensors ``q_bias``, ``k_bias``, ``v_bias``, ``out_bias``), values of a size ``vdim`` of their own, a
-    softmax scale given by the configuration, and an optional chunked mask: with ``chunk`` = c a query at position i
-    reads key j <= i only if floor(i / c) = floor(j / c), chunks counted from position 0 of the sequence (so the mask
-    does not depend on how a prompt was cut into steps). Query head h reads key/value head h // (heads / kv_heads).
+def distance_bucket(distance: int, buckets: int, far: float) -> int:
+    """The row of a table of ``buckets`` learned score biases that stands for a key ``distance`` positions back: the
+    first buckets // 2 rows stand for one distance each, the others divide the distances from buckets // 2 up to
+    ``far`` evenly in the logarithm, the last row takes everything farther (the bucketing of relative positions in
+    Raffel et al., "Exploring the Limits of Transfer Learning with a Unified Text-to-Text Transformer", 2020, for one
+    direction)."""
+    exact = buckets // 2
+    if distance < exact:
+        return distance
+    stretched = exact + int(math.floor(math.log(distance / exact) / math.log(far / exact) * (buckets - exact)))
+    return min(buckets - 1, stretched)
 
-    One fused [q | k | v] projection leaves float32 sums; one launch adds the biases, rounds once and writes q to its
-    buffer and k and v to the paged cache. On the bfloat16 path, when keys and values differ in size and the
-    tensor-core kernels take the larger size, both are stored at that size (the tails zero: a zero adds nothing to a
-    score, and a zero value column gives a zero result column, which meets zero columns of the output projection);
-    otherwise heads are stored as they are and the general kernel reads values of their own size."""
+
+def distance_bias_table(table: torch.Tensor, far: int) -> torch.Tensor:
+    """A stored table [buckets, heads] as the attention kernels read it: float32 [heads, far + 1], entry [h, n] the bias
+    of a key n positions back (``far`` and everything farther share the last entry, whose bucket is the last)."""
+    buckets = int(table.shape[0])
+    if buckets < 2 or far <= buckets // 2:
+        raise ValueError(f"a distance table of {buckets} rows up to distance {far}: needs 2 rows or more and a "
+                         f"farthest distance beyond {buckets // 2}")
+    rows = torch.tensor([distance_bucket(n, buckets, float(far)) for n in range(far + 1)], dtype=torch.long)
+    return table.to(torch.float32)[rows].t().contiguous()
+
+
+@register_part("mixer", "prepared_attention")
+class PreparedAttentionMixer(PagedAttentionKernels):
+    """Causal grouped-query softmax attention whose q, k and v leave one fused projection as float32 sums and are
+    made ready for the paged attention kernels by one launch. Everything but the four matrices is optional:
+
+    * biases on the projections (tensors ``q_bias``, ``k_bias``, ``v_bias``, ``out_bias``);
+    * ``whole_qk_norm``: one RMS norm over the whole q projection and one over the whole k projection (tensors
+      ``q_norm``, ``k_norm`` as wide as the projections, ``eps``);
+    * a nested part ``position`` that rotates pairs (i, i + half) of the heads' leading dimensions;
+    * ``temperature`` = {coef, every}: q times 1 + coef ln(floor((position + 1) / every) + 1);
+    * ``distance_far`` with the tensor ``distance_table`` [buckets, heads]: a learned number per head and distance
+      bucket (:func:`distance_bucket`) added to the scaled scores;
+    * ``value_mix``: "first" notes the layer's values of the step's tokens for later layers, "blend" replaces v by
+      (1 - lam) v + lam v_first with lam the stored number ``value_mix`` (what is cached is the blended v);
+    * ``output_gate``: the heads' results times sigmoid(W_g h), element by element (tensor ``gate``);
+    * values of a size ``vdim`` of their own, a softmax scale given by the configuration, a sink per head (tensor
+      ``sinks``), and a mask: ``window`` = w lets a query at position i read key j when 0 <= i - j < w, ``chunk`` = c
+      when floor(i / c) = floor(j / c) (chunks counted from position 0 of the sequence, so the mask does not depend
+      on how a prompt was cut into steps). Query head h reads key/value head h // (heads / kv_heads).
+
+    On the bfloat16 path, when keys and values differ in size and the tensor-core kernels take the larger size, both
+    are stored at that size (the tails zero: a zero adds nothing to a score, and a zero value column gives a zero
+    result column, which meets zero columns of the output projection); otherwise heads are stored as they are and
+    the general kernel reads values of their own size."""
 
     def __init__(self, params: Mapping, weights: Mapping[str, torch.Tensor], parts: Mapping, rt: Runtime):
         self.rt = rt
@@ -365,26 +401,74 @@ class ChunkedAttentionMixer(PagedAttentionKernels):
         chunk = params.get("chunk")
         self.chunk = int(chunk) if chunk else None
         if self.chunk is not None and self.chunk < 1:
-            raise ValueError(f"chunked_attention: a chunk of {self.chunk} positions")
+            raise ValueError(f"attention: a chunk of {self.chunk} positions")
+        window = params.get("window")
+        self.window = int(window) if window else None
+        if self.window is not None and (self.window < 1 or self.chunk is not None):
+            raise ValueError(f"attention: a window of {self.window} positions (beside a chunk: {self.chunk})")
         if self.heads % self.kv_heads:
             raise ValueError(f"{self.heads} query heads are not a multiple of {self.kv_heads} kv heads")
-        self.window = None
-        self.sinks = None
+        self.sinks = rt.vector(weights["sinks"]) if "sinks" in weights else None
+        if self.sinks is not None and self.sinks.shape != (self.heads,):
+            raise ValueError(f"attention sinks have shape {tuple(self.sinks.shape)}, expected ({self.heads},)")
+        self.output_gate = bool(params.get("output_gate", False))
         # sizes of a stored head: what the kernels see as head size (keys, queries) and value size
         self.head_dim = self.value_dim = None
         larger = max(self.dim, self.vdim)
-        if self.dim == self.vdim or (rt.act_dtype == torch.bfloat16 and self._fast_kernels_take(larger)):
+        if self.dim == self.vdim or (rt.act_dtype == torch.bfloat16 and not self.output_gate
+                                     and self._fast_kernels_take(larger)):
             self.head_dim = self.value_dim = larger
         else:
             self.head_dim, self.value_dim = self.dim, self.vdim
         q_width, k_width, v_width = self.heads * self.dim, self.kv_heads * self.dim, self.kv_heads * self.vdim
-        self.w_qkv = rt.matrix(torch.cat([weights["q"], weights["k"], weights["v"]], dim=0))
+        self.q_width, self.k_width, self.v_width = q_width, k_width, v_width
+        stacked = [weights["q"], weights["k"], weights["v"]]
+        if self.output_gate:
+            stacked.append(weights["gate"])
+        self.w_qkv = rt.matrix(torch.cat(stacked, dim=0))
+        self.gate_width = self.heads * self.vdim if self.output_gate else 0
         biases = [weights.get("q_bias"), weights.get("k_bias"), weights.get("v_bias")]
         if any(b is not None for b in biases):
             widths = (q_width, k_width, v_width)
             self.bias = rt.vector(torch.cat([b.float() if b is not None else torch.zeros(w) for b, w in zip(biases, widths)]))
         else:
             self.bias = None
+        # what the plain store (biases only) cannot do goes through the general preparation
+        self.whole_qk_norm = bool(params.get("whole_qk_norm", False))
+        self.eps = float(params.get("eps", 1e-6))
+        self.q_norm = self.k_norm = None
+        if self.whole_qk_norm:
+            self.q_norm, self.k_norm = rt.vector(weights["q_norm"]), rt.vector(weights["k_norm"])
+            if self.q_norm.shape != (q_width,) or self.k_norm.shape != (k_width,):
+                raise ValueError(f"whole-projection norm weights of shapes {tuple(self.q_norm.shape)} / "
+                                 f"{tuple(self.k_norm.shape)}, expected ({q_width},) / ({k_width},)")
+        position = parts.get("position")
+        fused = position.fused() if position is not None else None
+        self.frequencies, self.rotary_dim = None, 0
+        if fused is not None and fused.get("rotary_dim"):
+            if fused.get("interleaved") or fused["rotary_dim"] > self.dim:
+                raise ValueError("attention: the position part must rotate pairs (i, i + half) of at most dim dimensions")
+            self.frequencies, self.rotary_dim = fused["inv_freq"], int(fused["rotary_dim"])
+        elif position is not None and fused is None:
+            raise ValueError("attention: the position part must offer fused() tables")
+        temperature = params.get("temperature")
+        self.temperature = (float(temperature["coef"]), int(temperature["every"])) if temperature else None
+        if self.temperature is not None and self.temperature[1] < 1:
+            raise ValueError(f"attention: a query temperature every {self.temperature[1]} positions")
+        self.distance_bias = None
+        if "distance_table" in weights:
+            table = weights["distance_table"]
+            if table.dim() != 2 or table.shape[1] != self.heads:
+                raise ValueError(f"a distance table of shape {tuple(table.shape)}, expected (buckets, {self.heads})")
+            self.distance_bias = rt.vector(distance_bias_table(table, int(params["distance_far"])))
+        mix = params.get("value_mix")
+        if mix not in (None, "first", "blend"):
+            raise ValueError(f"attention: value_mix {mix!r}; known: first, blend")
+        self.blend = {None: 0, "first": 1, "blend": 2}[mix]
+        self.lam = float(weights["value_mix"].to(torch.float32).reshape(-1)[0]) if self.blend == 2 else 0.0
+        # the first marked layer's values of the step's tokens: float32 rows that every marked layer of a model shares
+        self.first_values = rt.scratch("attention.first_values", v_width, torch.float32) if self.blend else None
+        self.prepares = bool(self.whole_qk_norm or self.frequencies is not None or self.temperature or self.blend)
         w_out = weights["out"]
         if self.value_dim != self.vdim:          # zero columns where the attention's result has its zero tail
             padded = torch.zeros((w_out.shape[0], self.heads, self.value_dim), dtype=w_out.dtype)
@@ -392,35 +476,47 @@ class ChunkedAttentionMixer(PagedAttentionKernels):
             w_out = padded.reshape(w_out.shape[0], self.heads * self.value_dim)
         self.w_out = rt.matrix(w_out)
         self.out_bias = rt.vector(weights["out_bias"]) if "out_bias" in weights else None
+        self.ends_with_product = self.out_bias is None       # forward() then writes `out` last, with rt.linear
         self.binding: Optional[PagedBinding] = None
         self._resident_blocks: Optional[int] = None
-        self.projected = rt.scratch("chunked_attention.proj", q_width + k_width + v_width, torch.float32)
+        self.projected = rt.scratch("prepared_attention.proj", q_width + k_width + v_width + self.gate_width, torch.float32)
         self.qkv_width = self.heads * self.head_dim
-        self.qkv = rt.scratch("chunked_attention.q", self.qkv_width)
-        self.attended = rt.scratch("chunked_attention.out", self.heads * self.value_dim)
-        self.unbiased = rt.scratch("chunked_attention.unbiased", self.hidden, torch.float32) if self.out_bias is not None else None
+        self.qkv = rt.scratch("prepared_attention.q", self.qkv_width)
+        self.attended = rt.scratch("prepared_attention.out", self.heads * self.value_dim)
+        self.unbiased = rt.scratch("prepared_attention.unbiased", self.hidden, torch.float32) if self.out_bias is not None else None
 
     def _fast_kernels_take(self, size: int) -> bool:
         return (kernels.attention_prefill_supported(self.heads, self.kv_heads, size, torch.bfloat16)
                 and kernels.attention_decode_supported(self.heads, self.kv_heads, size, torch.bfloat16))
 
     def cache_need(self):
-        return PagedNeed(kv_heads=self.kv_heads, head_dim=self.head_dim, window=None,
+        return PagedNeed(kv_heads=self.kv_heads, head_dim=self.head_dim, window=self.window,
                          value_head_dim=None if self.value_dim == self.head_dim else self.value_dim)
 
     def bind_cache(self, binding: PagedBinding) -> None:
         if not binding.owner:
-            raise ValueError("chunked_attention writes its keys and values: it cannot read another position's cache")
+            raise ValueError("this attention writes its keys and values: it cannot read another position's cache")
         self.binding = binding
 
     def _attend(self, x: torch.Tensor, step: StepContext) -> None:
         rt, b, t = self.rt, self.binding, step.tokens
         rt.linear(x, self.w_qkv, self.projected, t)
         table = step.block_tables[b.group]
-        kernels.bias_store_kv(self.projected, self.bias, self.qkv, step.positions, step.token_span, table, b.k, b.v, t,
-                              self.heads, self.kv_heads, self.dim, self.vdim, self.head_dim, self.value_dim,
-                              b.page_tokens, step.error_flag)
+        if self.prepares:
+            kernels.qkv_prepare(self.projected, self.bias, self.qkv, step.positions, step.token_span, table, b.k, b.v, t,
+                                self.heads, self.kv_heads, self.dim, self.vdim, self.head_dim, self.value_dim,
+                                b.page_tokens, step.error_flag, q_norm=self.q_norm, k_norm=self.k_norm,
+                                norm_eps=self.eps, frequencies=self.frequencies, rotary_dim=self.rotary_dim,
+                                temperature=self.temperature, blend=self.blend, lam=self.lam,
+                                first_values=self.first_values)
+        else:
+            kernels.bias_store_kv(self.projected, self.bias, self.qkv, step.positions, step.token_span, table, b.k, b.v,
+                                  t, self.heads, self.kv_heads, self.dim, self.vdim, self.head_dim, self.value_dim,
+                                  b.page_tokens, step.error_flag)
         self.attend(step, table)
+        if self.output_gate:
+            kernels.sigmoid_gate(self.attended, self.projected[:, self.q_width + self.k_width + self.v_width:], t,
+                                 self.gate_width)
 
     def forward_without_bias(self, x: torch.Tensor, out: torch.Tensor, step: StepContext) -> Optional[torch.Tensor]:
         """forward() into a float32 ``out`` without the output projection's bias, which is returned (or None) for a
@@ -436,6 +532,12 @@ class ChunkedAttentionMixer(PagedAttentionKernels):
             return
         self.forward_without_bias(x, self.unbiased, step)
         kernels.scaled_sum(self.unbiased, None, self.out_bias, 1.0, 0.0, out, step.tokens)
+
+
+@register_part("mixer", "chunked_attention")
+class ChunkedAttentionMixer(PreparedAttentionMixer):
+    """The prepared attention as a design names it that uses it for its chunked mask: no position encoding, biases on
+    the four projections, values of a size of their own, ``chunk`` positions a chunk."""
 
 
 @register_part("mixer", "side_by_side")

@@ -75,3 +75,22 @@ class DynamicTanh:
     def add_norm_pair(self, residual: torch.Tensor, delta: Optional[torch.Tensor], delta_b: Optional[torch.Tensor],
                       other: "DynamicTanh", out: torch.Tensor, other_out: torch.Tensor, n_rows: int) -> None:
         kernels.add_dyt(residual, delta, delta_b, n_rows, self._terms(out), other._terms(other_out))
+
+
+@register_part("norm", "layernorm")
+class LayerNorm:
+    """y = (x - mean(x)) / sqrt(var(x) + eps) * w (+ b), var the mean of the squared deviations from the mean (Ba,
+    Kiros and Hinton, "Layer Normalization", 2016); the tensor ``bias`` is optional. Sums in float32, two passes."""
+
+    def __init__(self, params: Mapping, weights: Mapping[str, torch.Tensor], rt: Runtime):
+        self.width = int(params["width"])
+        self.eps = float(params["eps"])
+        self.weight = rt.vector(weights["weight"])
+        self.bias = rt.vector(weights["bias"]) if "bias" in weights else None
+        for name, vector in (("weight", self.weight), ("bias", self.bias)):
+            if vector is not None and vector.shape != (self.width,):
+                raise ValueError(f"layernorm {name} has shape {tuple(vector.shape)}, expected ({self.width},)")
+
+    def add_norm(self, residual: torch.Tensor, delta: Optional[torch.Tensor], out: torch.Tensor, n_rows: int,
+                 rows: Optional[torch.Tensor] = None) -> None:
+        kernels.add_layernorm(residual, delta, self.weight, out, self.eps, rows=rows, n_rows=n_rows, bias=self.bias)

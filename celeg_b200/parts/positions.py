@@ -24,7 +24,8 @@ class SplitHalfRope:
     Frequencies are computed in double and rounded to float32, the angle product and
     sin/cos are float32, as celeg's CPU kernel does (src/backend/cpu/kernels/rope.cpp:74-79;
     include/celeg/model/position.hpp:77-78). ``wavelength_scaling`` = {factor, low, high, original}
-    rescales the frequencies (:func:`scale_by_wavelength`)."""
+    rescales the frequencies (:func:`scale_by_wavelength`); ``linear_factor`` divides every frequency by a constant
+    (positions counted in units of that many tokens)."""
 
     def __init__(self, params: Mapping, rt: Runtime):
         self.theta = float(params["theta"])
@@ -39,6 +40,11 @@ class SplitHalfRope:
         if scaling:
             frequencies = scale_by_wavelength(frequencies, float(scaling["factor"]), float(scaling["low"]),
                                               float(scaling["high"]), float(scaling["original"]))
+        linear = params.get("linear_factor")
+        if linear is not None:
+            if float(linear) <= 0:
+                raise ValueError(f"linear_factor {linear} must be positive")
+            frequencies = frequencies / float(linear)
         self.inv_freq = frequencies.to(torch.float32).to(rt.device)
 
     def fused(self) -> Optional[dict]:
