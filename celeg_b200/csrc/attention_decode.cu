@@ -105,7 +105,7 @@ static int attention_decode_checked(const void* q, int q_row_stride, void* out, 
                                     int chunk, int max_splits, float* partial_o, float* partial_ml, int* counters,
                                     int* error_flag, int fuse_qk, const float* q_norm_w, const float* k_norm_w,
                                     const float* inv_freq, int rotary_dim, float norm_eps, const float* sinks,
-                                    cudaStream_t stream) {
+                                    cudaStream_t stream, const float* distance_bias = nullptr, int distance_last = 0) {
     CELEG_REQUIRE(tokens >= 0 && q_heads > 0 && kv_heads > 0 && head_dim > 0 && page_tokens > 0,
                   "attention_decode: invalid sizes tokens=%d q_heads=%d kv_heads=%d head_dim=%d page_tokens=%d",
                   tokens, q_heads, kv_heads, head_dim, page_tokens);
@@ -152,6 +152,8 @@ static int attention_decode_checked(const void* q, int q_row_stride, void* out, 
     p.counters = counters;
     p.error_flag = error_flag;
     p.sinks = sinks;
+    p.distance_bias = distance_bias;
+    p.distance_last = distance_last;
     p.fuse_qk = fuse_qk;
     p.q_norm_w = q_norm_w;
     p.k_norm_w = k_norm_w;
@@ -229,6 +231,22 @@ CELEG_API int celeg_attention_decode_sinks(const void* q, int q_row_stride, void
                                     block_table, table_stride, tokens, q_heads, kv_heads, head_dim, page_tokens, window,
                                     scale, chunk, max_splits, partial_o, partial_ml, counters, error_flag, 0, nullptr,
                                     nullptr, nullptr, 0, 0.0f, sinks, stream);
+}
+
+// The same with a sink per query head (or null) and a table of score biases by distance per query head,
+// [q_heads, distance_last + 1] float32 (or null): entry [h, min(n, distance_last)] joins head h's scaled score of
+// a key n positions back.
+CELEG_API int celeg_attention_decode_biased(const void* q, int q_row_stride, void* out, const void* k_cache,
+                                            const void* v_cache, long long page_stride, const int* positions,
+                                            const int* token_span, const int* block_table, int table_stride,
+                                            int tokens, int q_heads, int kv_heads, int head_dim, int page_tokens,
+                                            int window, float scale, int chunk, int max_splits, float* partial_o,
+                                            float* partial_ml, int* counters, int* error_flag, const float* sinks,
+                                            const float* distance_bias, int distance_last, cudaStream_t stream) {
+    return attention_decode_checked(q, q_row_stride, out, k_cache, v_cache, page_stride, positions, token_span,
+                                    block_table, table_stride, tokens, q_heads, kv_heads, head_dim, page_tokens, window,
+                                    scale, chunk, max_splits, partial_o, partial_ml, counters, error_flag, 0, nullptr,
+                                    nullptr, nullptr, 0, 0.0f, sinks, stream, distance_bias, distance_last);
 }
 
 // The same with the q/k post-processing of the step's tokens done inside: qkv holds the raw projection

@@ -47,6 +47,8 @@ struct DecodeParams {
     int* counters;                 // [tokens, kv_heads], zero between launches
     int* error_flag;
     const float* sinks;            // [q_heads] or null: a score per head that enters the denominator once (no key, no value)
+    const float* distance_bias;    // [q_heads, distance_last + 1] or null: added to the scaled score by distance back
+    int distance_last;
     // Optional: the q/k post-processing of the step's own token done here instead of by a kernel of its
     // own. Then q (and the k and v behind it in the same rows: [q heads | k heads | v heads]) is the raw
     // projection; an item normalises and rotates its query heads itself, and the item whose keys include
@@ -335,7 +337,13 @@ __device__ __forceinline__ void attention_decode_item(const DecodeParams& p, con
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
                 const int key = tile_begin + nt * 8 + c2 + (e & 1);
-                const float v = key < end ? s[nt][e] * scale_log2 : -INFINITY;
+                float v = key < end ? s[nt][e] * scale_log2 : -INFINITY;
+                if (p.distance_bias && key < end) {
+                    // a learned number per (head, distance back to the key) joins the scaled score, in units of log2
+                    const int row = min(g + (e >> 1) * 8, group - 1);      // (rows past the group are never stored)
+                    v += __ldg(p.distance_bias + (size_t)(kvh * group + row) * (p.distance_last + 1) +
+                               max(0, min(pos - key, p.distance_last))) * 1.4426950408889634f;
+                }
                 s[nt][e] = v;
                 tile_max[e >> 1] = fmaxf(tile_max[e >> 1], v);
             }
@@ -718,7 +726,13 @@ __device__ __forceinline__ void attention_decode_item_solo(const DecodeParams& p
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
                 const int key = tile_begin + nt * 8 + c2 + (e & 1);
-                const float v = key < end ? s[nt][e] * scale_log2 : -INFINITY;
+                float v = key < end ? s[nt][e] * scale_log2 : -INFINITY;
+                if (p.distance_bias && key < end) {
+                    // a learned number per (head, distance back to the key) joins the scaled score, in units of log2
+                    const int row = min(g + (e >> 1) * 8, group - 1);      // (rows past the group are never stored)
+                    v += __ldg(p.distance_bias + (size_t)(kvh * group + row) * (p.distance_last + 1) +
+                               max(0, min(pos - key, p.distance_last))) * 1.4426950408889634f;
+                }
                 s[nt][e] = v;
                 tile_max[e >> 1] = fmaxf(tile_max[e >> 1], v);
             }

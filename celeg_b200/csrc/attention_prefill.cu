@@ -10,9 +10,9 @@
 //   denominator in float32, exponentials by exp2 of pre-scaled scores).
 //
 // Any head size that is a multiple of 8 up to 256 (padded with zeros to 64, 128 or 256 in shared
-// memory), any number of heads and groups, any page size, optional window. A token's keys are
-// those of its own request at positions <= its own, whether they were written by this step or by
-// earlier ones.
+// memory), any number of heads and groups, any page size, optional window, optional table of score biases by
+// distance (query position minus key position) per head. A token's keys are those of its own request at
+// positions <= its own, whether they were written by this step or by earlier ones.
 //
 // Counterparts in celeg: the ragged path runs gqa_decode_paged_batch_kernel with one block per
 // (token, head) walking all keys (src/backend/cuda/kernels/attention_paged.cuh:3-166); its
@@ -40,6 +40,8 @@ struct PrefillParams {
     int spans, q_heads, kv_heads, head_dim, page_tokens, window;
     float scale_log2;              // softmax scale * log2(e)
     const float* sinks;            // [q_heads] or null: a score per head in the denominator, no key, no value
+    const float* distance_bias;    // [q_heads, distance_last + 1] or null: added to the scaled score by distance back
+    int distance_last;
     int* error_flag;
 };
 
@@ -180,7 +182,25 @@ __global__ void __launch_bounds__(kPrefillThreads, D_PAD <= 64 ? 2 : 1) attentio
         const int warp_first_pos = pos0 + warp * 16;
         const bool full_tile = kb * kBlockN + kBlockN - 1 <= warp_first_pos && warp * 16 + 15 < rows &&
                                kb * kBlockN >= first_visible_key(warp_first_pos + 15, p.window);
-        if (full_tile) {
+        if (p.distance_bias) {
+            // a learned number per (head, distance back to the key) joins the scaled score, in units of log2
+            const float* bias = p.distance_bias + (size_t)h * (p.distance_last + 1);
+#pragma unroll
+            for (int nt = 0; nt < kBlockN / 8; ++nt) {
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const int row = q_row + (e >> 1) * 8;
+                    const int key = kb * kBlockN + nt * 8 + c2 + (e & 1);
+                    const int qpos = pos0 + row;
+                    const bool valid = row < rows && key <= qpos && key >= first_visible_key(qpos, p.window);
+                    const float v = valid ? s[nt][e] * p.scale_log2 +
+                                                __ldg(bias + max(0, min(qpos - key, p.distance_last))) * 1.4426950408889634f
+                                          : -INFINITY;
+                    s[nt][e] = v;
+                    tile_max[e >> 1] = fmaxf(tile_max[e >> 1], v);
+                }
+            }
+        } else if (full_tile) {
 #pragma unroll
             for (int nt = 0; nt < kBlockN / 8; ++nt) {
 #pragma unroll
@@ -301,7 +321,8 @@ CELEG_API int celeg_attention_prefill(const void* q, int q_row_stride, void* out
                                       const void* v_cache, long long page_stride, const int* positions,
                                       const int* span_begin, const int* block_table, int table_stride,
                                       int tokens, int spans, int q_heads, int kv_heads, int head_dim,
-                                      int page_tokens, int window, float scale, const float* sinks, int* error_flag,
+                                      int page_tokens, int window, float scale, const float* sinks,
+                                      const float* distance_bias, int distance_last, int* error_flag,
                                       cudaStream_t stream) {
     CELEG_REQUIRE(tokens >= 0 && spans >= 0 && q_heads > 0 && kv_heads > 0 && head_dim > 0 && page_tokens > 0,
                   "attention_prefill: invalid sizes tokens=%d spans=%d q_heads=%d kv_heads=%d head_dim=%d "
@@ -333,6 +354,8 @@ CELEG_API int celeg_attention_prefill(const void* q, int q_row_stride, void* out
     p.window = window;
     p.scale_log2 = scale * 1.4426950408889634f;
     p.sinks = sinks;
+    p.distance_bias = distance_bias;
+    p.distance_last = distance_last;
     p.error_flag = error_flag;
     const int tiles = (tokens + kBlockM - 1) / kBlockM + spans;      // upper bound on sum of ceil(len / 64)
     if (head_dim <= 64) return launch_prefill<64>(p, tiles, stream);

@@ -56,6 +56,11 @@ struct FaParams {
     int spans, q_heads, kv_heads, page_tokens, window;
     float scale_log2;              // softmax scale * log2(e)
     const float* sinks;            // [q_heads] or null: a score per head in every row's denominator, no key, no value
+    // [q_heads, distance_last + 1] or null: entry [h, min(n, distance_last)] joins head h's scaled score of a key n
+    // positions back; bias_factor = 1 / scale brings it to the unit of the raw scores
+    const float* distance_bias;
+    int distance_last;
+    float bias_factor;
     int* error_flag;
 };
 
@@ -263,6 +268,13 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
                         sc[32 + j] = __uint_as_float(hi[j]);
                     }
                 }
+                if (p.distance_bias) {
+                    const float* bias = p.distance_bias + (size_t)h * (p.distance_last + 1);
+                    const int back = qpos - key_base;               // key key_base + j lies back - j positions back
+#pragma unroll
+                    for (int j = 0; j < kFaN; ++j)
+                        sc[j] = fmaf(__ldg(bias + max(0, min(back - j, p.distance_last))), p.bias_factor, sc[j]);
+                }
                 if (!full) {
                     // keys key_base + [lo, hi] are the ones this row sees
                     const int hi = live ? min(kFaN - 1, qpos - key_base) : -1;
@@ -404,7 +416,10 @@ CELEG_API int celeg_attention_prefill_tcgen05(const void* q, int q_row_stride, i
                                               const int* span_begin, const int* block_table, int table_stride,
                                               int tokens, int spans, int tile_count, int q_heads, int kv_heads,
                                               int head_dim, int page_tokens, int window, float scale,
-                                              const float* sinks, int* error_flag, cudaStream_t stream) {
+                                              const float* sinks, const float* distance_bias, int distance_last,
+                                              int* error_flag, cudaStream_t stream) {
+    CELEG_REQUIRE(!distance_bias || scale > 0.0f, "attention_prefill_tcgen05: score biases need a positive scale, got %g",
+                  scale);
     CELEG_REQUIRE(celeg_attention_prefill_tcgen05_supported(q_heads, kv_heads, head_dim, page_tokens),
                   "attention_prefill_tcgen05: head_dim=%d page_tokens=%d q_heads=%d kv_heads=%d are not taken here",
                   head_dim, page_tokens, q_heads, kv_heads);
@@ -432,6 +447,9 @@ CELEG_API int celeg_attention_prefill_tcgen05(const void* q, int q_row_stride, i
     p.window = window;
     p.scale_log2 = scale * 1.4426950408889634f;
     p.sinks = sinks;
+    p.distance_bias = distance_bias;
+    p.distance_last = distance_last;
+    p.bias_factor = distance_bias ? 1.0f / scale : 0.0f;
     p.error_flag = error_flag;
     const cudaError_t status = cudaFuncSetAttribute(attention_prefill_tcgen05_kernel,
                                                     cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kFaSmemBytes);

@@ -84,10 +84,13 @@ _SIGNATURES = {
     "celeg_attention_decode_resident_blocks": [c_int],
     "celeg_attention_prefill": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_longlong, c_void_p, c_void_p,
                                 c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float,
-                                c_void_p, c_void_p, c_void_p],
+                                c_void_p, c_void_p, c_int, c_void_p, c_void_p],
     "celeg_attention_prefill_tcgen05": [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
                                         c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
-                                        c_float, c_void_p, c_void_p, c_void_p],
+                                        c_float, c_void_p, c_void_p, c_int, c_void_p, c_void_p],
+    "celeg_attention_decode_biased": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_longlong, c_void_p, c_void_p,
+                                      c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int,
+                                      c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p],
     "celeg_gemv_bf16": [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_int,
                         c_void_p, c_longlong, c_void_p, c_void_p],
     "celeg_gemv_prefetch_next": [c_void_p, c_longlong],
@@ -449,7 +452,8 @@ def attention_decode(q: torch.Tensor, q_row_stride: int, out: torch.Tensor, k_ca
                      block_table: torch.Tensor, tokens: int, q_heads: int, kv_heads: int, head_dim: int,
                      page_tokens: int, window: Optional[int], scale: float, chunk: int, max_splits: int,
                      partial_o: torch.Tensor, partial_ml: torch.Tensor, counters: torch.Tensor,
-                     error_flag: torch.Tensor, sinks: Optional[torch.Tensor] = None) -> None:
+                     error_flag: torch.Tensor, sinks: Optional[torch.Tensor] = None,
+                     distance_bias: Optional[torch.Tensor] = None) -> None:
     """One query token per row, keys split into chunks of ``chunk``; scratch: partial_o float32
     [tokens*q_heads*max_splits*head_dim], partial_ml float32 [tokens*q_heads*max_splits*2],
     counters int32 [tokens*kv_heads] (zero before the first call, left zero by every call).
@@ -458,6 +462,16 @@ def attention_decode(q: torch.Tensor, q_row_stride: int, out: torch.Tensor, k_ca
     assert partial_o.numel() >= tokens * q_heads * max_splits * head_dim
     assert partial_ml.numel() >= tokens * q_heads * max_splits * 2
     assert counters.numel() >= tokens * kv_heads
+    if distance_bias is not None:
+        if sinks is not None:
+            _need(sinks, torch.float32, "sinks")
+        bias_ptr, bias_last = _distance_bias(distance_bias, q_heads)
+        _check(library().celeg_attention_decode_biased(
+            _ptr(q), q_row_stride, _ptr(out), _ptr(k_cache), _ptr(v_cache), k_cache.stride(0), _ptr(positions),
+            _ptr(token_span), _ptr(block_table), block_table.stride(0), tokens, q_heads, kv_heads, head_dim,
+            page_tokens, int(window or 0), scale, chunk, max_splits, _ptr(partial_o), _ptr(partial_ml),
+            _ptr(counters), _ptr(error_flag), _ptr(sinks), bias_ptr, bias_last, _stream()))
+        return
     if sinks is not None:
         _need(sinks, torch.float32, "sinks")
         _check(library().celeg_attention_decode_sinks(
@@ -499,13 +513,15 @@ def attention_prefill(q: torch.Tensor, q_row_stride: int, out: torch.Tensor, k_c
                       v_cache: torch.Tensor, positions: torch.Tensor, span_begin: torch.Tensor,
                       block_table: torch.Tensor, tokens: int, spans: int, q_heads: int, kv_heads: int,
                       head_dim: int, page_tokens: int, window: Optional[int], scale: float,
-                      error_flag: torch.Tensor, sinks: Optional[torch.Tensor] = None) -> None:
+                      error_flag: torch.Tensor, sinks: Optional[torch.Tensor] = None,
+                      distance_bias: Optional[torch.Tensor] = None) -> None:
     if sinks is not None:
         _need(sinks, torch.float32, "sinks")
+    bias_ptr, bias_last = _distance_bias(distance_bias, q_heads)
     _check(library().celeg_attention_prefill(
         _ptr(q), q_row_stride, _ptr(out), _ptr(k_cache), _ptr(v_cache), k_cache.stride(0), _ptr(positions),
         _ptr(span_begin), _ptr(block_table), block_table.stride(0), tokens, spans, q_heads, kv_heads, head_dim,
-        page_tokens, int(window or 0), scale, _ptr(sinks), _ptr(error_flag), _stream()))
+        page_tokens, int(window or 0), scale, _ptr(sinks), bias_ptr, bias_last, _ptr(error_flag), _stream()))
 
 
 def attention_prefill_tcgen05_supported(q_heads: int, kv_heads: int, head_dim: int, page_tokens: int,
@@ -519,17 +535,19 @@ def attention_prefill_tcgen05(q: torch.Tensor, q_row_stride: int, out: torch.Ten
                               v_cache: torch.Tensor, positions: torch.Tensor, span_begin: torch.Tensor,
                               block_table: torch.Tensor, tokens: int, spans: int, tile_count: int, q_heads: int,
                               kv_heads: int, head_dim: int, page_tokens: int, window: Optional[int], scale: float,
-                              error_flag: torch.Tensor, sinks: Optional[torch.Tensor] = None) -> None:
+                              error_flag: torch.Tensor, sinks: Optional[torch.Tensor] = None,
+                              distance_bias: Optional[torch.Tensor] = None) -> None:
     """Prompt-portion attention on tcgen05 (S and O' in tensor memory, Q/K/V by TMA).
-    ``tile_count`` = sum over the spans of ceil(length / 128)."""
+    ``tile_count`` = sum over the spans of ceil(length / 128). ``distance_bias``: as for :func:`attention_generic`."""
     if not (k_cache.is_contiguous() and v_cache.is_contiguous()):
         raise KernelLibraryError("attention_prefill_tcgen05 needs contiguous cache layers")
     if sinks is not None:
         _need(sinks, torch.float32, "sinks")
+    bias_ptr, bias_last = _distance_bias(distance_bias, q_heads)
     _check(library().celeg_attention_prefill_tcgen05(
         _ptr(q), q_row_stride, q.shape[0], _ptr(out), _ptr(k_cache), _ptr(v_cache), k_cache.shape[0], _ptr(positions),
         _ptr(span_begin), _ptr(block_table), block_table.stride(0), tokens, spans, tile_count, q_heads, kv_heads,
-        head_dim, page_tokens, int(window or 0), scale, _ptr(sinks), _ptr(error_flag), _stream()))
+        head_dim, page_tokens, int(window or 0), scale, _ptr(sinks), bias_ptr, bias_last, _ptr(error_flag), _stream()))
 
 
 ACT_GELU_ERF, ACT_GELU_TANH, ACT_SILU, ACT_RELU_SQUARED, ACT_RELU = 0, 1, 2, 3, 4      # codes of csrc/common.cuh: activate()

@@ -107,7 +107,8 @@ def decode_split(tokens: int, kv_heads: int, context_bucket: int, window: Option
 class PagedAttentionKernels:
     """The choice among the attention kernels for a step's queries over a paged cache, shared by the mixers that
     attend over one. A mixer that inherits it has ``rt``, ``heads``, ``kv_heads``, ``head_dim``, ``window``, ``scale``,
-    ``sinks`` (or None), ``binding``, the queries in ``qkv`` (head h of a row at h * head_dim, rows ``qkv_width``
+    ``sinks`` (or None), ``distance_bias`` (absent, None, or a float32 table [heads, n + 1] of score biases by distance
+    back to the key), ``binding``, the queries in ``qkv`` (head h of a row at h * head_dim, rows ``qkv_width``
     apart), the output buffer ``attended`` [tokens, heads * head_dim] and ``_resident_blocks = None``.
     ``_value_cache()`` names the tensor the values are read from: the binding's own, or the keys themselves for a
     mixer whose values are a leading part of what it caches as keys."""
@@ -152,7 +153,7 @@ class PagedAttentionKernels:
         among the query heads of a group and splits long contexts, where a prompt kernel would walk the whole
         context once per query head for one row of a 128-row tile."""
         rt = self.rt
-        if self._values_differ() or getattr(self, "distance_bias", None) is not None:
+        if self._values_differ():
             self._attend_general(step, table, 0)
             return
         if self._decodes(step):
@@ -173,7 +174,8 @@ class PagedAttentionKernels:
         kernels.attention_decode(self.qkv, self.qkv_width, self.attended, b.k, self._value_cache(), step.positions,
                                  step.token_span, table, count, self.heads, self.kv_heads,
                                  self.head_dim, b.page_tokens, self._mask(), self.scale, chunk, max_splits,
-                                 partial_o, partial_ml, counters, step.error_flag, sinks=self.sinks)
+                                 partial_o, partial_ml, counters, step.error_flag, sinks=self.sinks,
+                                 distance_bias=getattr(self, "distance_bias", None))
 
     def _attend_portions(self, step: StepContext, table: torch.Tensor, skip: int) -> None:
         """The spans from ``skip`` on (the spans before it have one token each, so span ``skip`` begins at token
@@ -193,13 +195,14 @@ class PagedAttentionKernels:
             kernels.attention_prefill_tcgen05(self.qkv, self.qkv_width, self.attended, b.k, values, step.positions,
                                               span_begin, span_table, step.tokens, spans, tiles, self.heads,
                                               self.kv_heads, self.head_dim, b.page_tokens, self._mask(), self.scale,
-                                              step.error_flag, sinks=self.sinks)
+                                              step.error_flag, sinks=self.sinks,
+                                              distance_bias=getattr(self, "distance_bias", None))
             return
         if kernels.attention_prefill_supported(self.heads, self.kv_heads, self.head_dim, rt.act_dtype):
             kernels.attention_prefill(self.qkv, self.qkv_width, self.attended, b.k, values, step.positions,
                                       span_begin, span_table, step.tokens, spans, self.heads, self.kv_heads,
                                       self.head_dim, b.page_tokens, self._mask(), self.scale, step.error_flag,
-                                      sinks=self.sinks)
+                                      sinks=self.sinks, distance_bias=getattr(self, "distance_bias", None))
             return
         self._attend_general(step, table, skip)
 

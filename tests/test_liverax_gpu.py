@@ -1,0 +1,577 @@
+"""The Liverax design in the engine against the plain float64 model of ``plain_liverax.py``: whole prompts, decoding
+token by token, portions down to two tokens, batches of unequal requests, pages and slots used again, keys just inside
+and just outside a window and far beyond the farthest distance bucket with weights that make one key show, the sink,
+the query factor across its steps, the blended values, the first tokens of a sequence, and greedy generation through
+``Engine``, the command line and the trace runner. float32 path to 2e-4 of the logits' spread, bfloat16 path to a few
+percent."""
+from __future__ import annotations
+
+import copy
+
+import numpy as np
+import pytest
+
+import liverax_models as lm
+import plain_liverax as plain
+
+pytestmark = pytest.mark.gpu
+
+LIMIT = {"float32": 2e-4, "bfloat16": 1.5e-1}
+TYPICAL = {"float32": 1e-4, "bfloat16": 5e-2}
+# how far a row of the plain model must move under a deliberate fault for the fault to count as shown: ten times the
+# float32 limit, and in bfloat16 twice what the single-layer models below are held to there
+SHOWS = {"float32": 2e-3, "bfloat16": 0.2}
+SINGLE_LAYER_LIMIT = {"float32": 2e-4, "bfloat16": 0.1}
+
+
+def spread_error(got: np.ndarray, want: np.ndarray) -> np.ndarray:
+    """Per row: rms of the difference (mean taken off) over the rms of the wanted row (mean taken off)."""
+    d = got - want
+    d = d - d.mean(-1, keepdims=True)
+    w = want - want.mean(-1, keepdims=True)
+    return np.sqrt((d ** 2).mean(-1)) / np.sqrt((w ** 2).mean(-1))
+
+
+def check(got, want, dtype, what, limit=None):
+    err = spread_error(np.asarray(got, dtype=np.float64), want)
+    worst = int(np.argmax(err))
+    assert err[worst] <= (limit or LIMIT[dtype]), f"{what}: row {worst} differs by {err[worst]:.3e} of the row's spread"
+    assert np.median(err) <= TYPICAL[dtype], f"{what}: half of the rows differ by {np.median(err):.3e} and more"
+
+
+@pytest.fixture(scope="module")
+def models(tmp_path_factory):
+    base = tmp_path_factory.mktemp("liverax")
+    out = {}
+    for name, (raw, seed) in lm.CONFIGS.items():
+        folder = str(base / name)
+        disk, tensors = lm.write_model(folder, raw, seed)
+        out[name] = (folder, disk, plain.as_float64(tensors))
+    return out
+
+
+def load(folder, dtype, **kw):
+    from celeg_b200.engine.loading import load_model
+    args = dict(dtype=dtype, max_requests=4, cache_tokens=1024, max_batched_tokens=512, max_context=512)
+    args.update(kw)
+    return load_model(folder, **args)
+
+
+def run_steps(loaded, steps):
+    """steps: lists of (request, tokens); every place is wanted. Returns {request: [its logits rows in order]}."""
+    from celeg_b200.engine.step import StepEntry
+    rows = {}
+    for step in steps:
+        step = [(name, tokens) for name, tokens in step if len(tokens) > 0]
+        entries = [StepEntry(name, list(tokens), list(range(len(tokens)))) for name, tokens in step]
+        logits = loaded.step.run(entries, auto_begin=True).cpu().numpy()
+        loaded.step.raise_on_device_error()
+        at = 0
+        for name, tokens in step:
+            rows.setdefault(name, []).append(logits[at:at + len(tokens)].copy())
+            at += len(tokens)
+    return {name: np.concatenate(parts) for name, parts in rows.items()}
+
+
+def cut(tokens, sizes):
+    out, at, i = [], 0, 0
+    while at < len(tokens):
+        n = sizes[i % len(sizes)]
+        out.append(tokens[at:at + n])
+        at += n
+        i += 1
+    return out
+
+
+def tokens_of(vocab, length, seed):
+    return np.random.default_rng(seed).integers(0, vocab, size=length).tolist()
+
+
+# ------------------------------------------------------------------------------------------ whole models
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", list(lm.CONFIGS))
+def test_whole_prompt_then_token_by_token(models, name, dtype):
+    folder, raw, tensors = models[name]
+    tokens = tokens_of(raw["vocab"], 90, 1)
+    want = plain.forward(raw, tensors, tokens)
+    loaded = load(folder, dtype)
+    whole = run_steps(loaded, [[("w", tokens)]])["w"]
+    check(whole, want, dtype, f"{name} whole")
+    loaded.step.end("w")
+    steps = [[("d", tokens[:37])]] + [[("d", [t])] for t in tokens[37:]]
+    decoded = run_steps(loaded, steps)["d"]
+    check(decoded, want, dtype, f"{name} prompt of 37 then token by token")
+    if dtype == "float32":       # how the prompt is cut changes nothing beyond rounding
+        assert np.abs(decoded - whole).max() <= 1e-3 * np.abs(whole).max()
+
+
+@pytest.mark.parametrize("name", list(lm.CONFIGS))
+def test_the_stream_after_every_layer(models, name, tmp_path):
+    """A model cut after its n-th layer, with ones for the final norm's scale and unit rows as its head, hands out
+    the stream itself (centred and divided by its spread): layer by layer against the plain model."""
+    import torch
+    folder, raw, tensors = models[name]
+    full = lm.CONFIGS[name][0]
+    tokens = tokens_of(raw["vocab"], 40, 21)
+    _, streams = plain.forward(raw, tensors, tokens, keep_layers=True)
+    width = raw["width"]
+    for depth in range(1, len(raw["layers"]) + 1):
+        short = dict(full, layers=full["layers"][:depth])
+        short.pop("logit_softcap", None)
+        kept = {key: torch.from_numpy(value).to(torch.bfloat16) for key, value in tensors.items()
+                if not key.startswith("l") or int(key[1:key.index(".")]) < depth}
+        kept["final.norm"] = torch.ones(width, dtype=torch.bfloat16)
+        head = torch.zeros((raw["vocab"], width), dtype=torch.bfloat16)
+        head[:width] = torch.eye(width)[:raw["vocab"]]
+        kept["head"] = head
+        cut_folder = str(tmp_path / f"{name}{depth}")
+        lm.write_model(cut_folder, short, 0, tensors=kept)
+        got = run_steps(load(cut_folder, "float32"), [[("a", tokens)]])["a"][:, :min(width, raw["vocab"])].astype(np.float64)
+        normed = plain.layer_norm(streams[depth - 1], np.ones(width), float(raw["norm"]["eps"]))[:, :got.shape[1]]
+        assert np.abs(got - normed).max() <= 5e-5 * np.abs(normed).max(), f"{name} after layer {depth - 1}"
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", list(lm.CONFIGS))
+def test_portions_of_several_sizes_down_to_two_tokens(models, name, dtype):
+    folder, raw, tensors = models[name]
+    tokens = tokens_of(raw["vocab"], 231, 2)
+    want = plain.forward(raw, tensors, tokens)
+    loaded = load(folder, dtype)
+    for sizes in ([2], [16, 3, 2, 33, 1, 64], [129, 2, 2, 50]):
+        got = run_steps(loaded, [[("p", part)] for part in cut(tokens, sizes)])["p"]
+        check(got, want, dtype, f"{name} in portions of {sizes}")
+        loaded.step.end("p")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", list(lm.CONFIGS))
+def test_batches_of_unequal_requests_equal_each_alone(models, name, dtype):
+    """Four requests of unequal length, portions of some beside single tokens of others, one left out of a step: the
+    blended values of a step's tokens belong to their own request."""
+    folder, raw, tensors = models[name]
+    requests = {key: tokens_of(raw["vocab"], n, 10 + n) for key, n in (("a", 150), ("b", 41), ("c", 7), ("d", 98))}
+    want = {key: plain.forward(raw, tensors, tokens) for key, tokens in requests.items()}
+    a, b, c, d = (requests[key] for key in "abcd")
+    steps = [[("a", a[:70]), ("b", b[:1]), ("c", c[:2])],
+             [("b", b[1:2]), ("a", a[70:71]), ("c", c[2:]), ("d", d[:33])],
+             [("d", d[33:34]), ("b", b[2:30]), ("a", a[71:149])],
+             [("a", a[149:]), ("b", b[30:]), ("d", d[34:])]]
+    loaded = load(folder, dtype)
+    got = run_steps(loaded, steps)
+    for key in requests:
+        check(got[key], want[key], dtype, f"{name} request {key} in a batch")
+    if dtype == "float32":
+        for key in requests:
+            loaded.step.end(key)
+        alone = run_steps(loaded, [[("a", a)]])["a"]
+        assert np.abs(alone - got["a"]).max() <= 1e-3 * np.abs(alone).max()
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["mixed", "odd"])
+def test_pages_and_slots_are_used_again(models, name, dtype):
+    """Two slots and a pool of 160 positions for six requests one after the other, two live at a time: every later
+    request sits in a slot and in pages that an earlier one has left full of its own keys."""
+    folder, raw, tensors = models[name]
+    loaded = load(folder, dtype, max_requests=2, cache_tokens=160)
+    lengths = [75, 60, 31, 80, 17, 66]
+    for turn in range(3):
+        pair = {f"x{2 * turn}": tokens_of(raw["vocab"], lengths[2 * turn], 20 + turn),
+                f"y{2 * turn}": tokens_of(raw["vocab"], lengths[2 * turn + 1], 30 + turn)}
+        (a, ta), (b, tb) = pair.items()
+        steps = [[(a, ta[:20]), (b, tb[:3])], [(a, ta[20:21]), (b, tb[3:])], [(a, ta[21:])]]
+        got = run_steps(loaded, steps)
+        for key, tokens in pair.items():
+            check(got[key], plain.forward(raw, tensors, tokens), dtype, f"turn {turn} request {key}")
+            loaded.step.end(key)
+        loaded.manager.check_invariants()
+    assert loaded.manager.free_slots == 2
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_long_portions_and_long_decoding(models, dtype):
+    """A prompt of 700 tokens (beyond every window, beyond the farthest distance bucket, several steps of the query
+    factor) in two portions beside another request, then 150 tokens one by one."""
+    folder, raw, tensors = models["wide"]
+    long_one, other = tokens_of(raw["vocab"], 850, 31), tokens_of(raw["vocab"], 300, 32)
+    want = {"a": plain.forward(raw, tensors, long_one), "b": plain.forward(raw, tensors, other)}
+    loaded = load(folder, dtype, cache_tokens=2048, max_batched_tokens=1024, max_context=1024)
+    steps = [[("b", other[:1]), ("a", long_one[:449])], [("b", other[1:2]), ("a", long_one[449:700])], [("b", other[2:])]]
+    steps += [[("a", [t])] for t in long_one[700:]]
+    got = run_steps(loaded, steps)
+    for key in want:
+        check(got[key], want[key], dtype, f"request {key} in long portions and long decoding")
+
+
+@pytest.mark.parametrize("name", ["mixed", "odd"])
+def test_long_decoding_from_the_first_token(models, name):
+    folder, raw, tensors = models[name]
+    tokens = tokens_of(raw["vocab"], 140, 5)
+    want = plain.forward(raw, tensors, tokens)
+    for dtype in ("float32", "bfloat16"):
+        got = run_steps(load(folder, dtype), [[("a", [t])] for t in tokens])["a"]
+        check(got, want, dtype, f"{name} decoded from its first token")
+
+
+def test_the_first_tokens_of_a_sequence(models):
+    """One token alone (its own key is all it sees, beside the sinks), then two, then three, as prompts and decoded."""
+    folder, raw, tensors = models["mixed"]
+    tokens = tokens_of(raw["vocab"], 3, 8)
+    want = plain.forward(raw, tensors, tokens)
+    loaded = load(folder, "float32")
+    for count in (1, 2, 3):
+        got = run_steps(loaded, [[("a", tokens[:count])]])["a"]
+        check(got, want[:count], "float32", f"a prompt of {count}", limit=2e-4)
+        loaded.step.end("a")
+    got = run_steps(loaded, [[("a", [t])] for t in tokens])["a"]
+    check(got, want, "float32", "three tokens one by one")
+
+
+# ------------------------------------------------------------------------------- mechanisms made to show
+def sharp_model(tmp_path, layer, seed, sharpen, width=48, vocab=96, ff=None):
+    raw = lm.single_layer(layer, ff, vocab=vocab, width=width)
+    folder = str(tmp_path / "sharp")
+    disk, tensors = lm.write_model(folder, raw, seed, sharpen=sharpen)
+    return folder, disk, plain.as_float64(tensors)
+
+
+def decode_and_prompt(folder, disk, tensors, tokens, dtype, what, split, **kw):
+    """The engine against the plain model, the prompt whole and then again with its tail decoded token by token."""
+    want = plain.forward(disk, tensors, tokens)
+    loaded = load(folder, dtype, **kw)
+    check(run_steps(loaded, [[("w", tokens)]])["w"], want, dtype, what + " (prompt)", limit=SINGLE_LAYER_LIMIT[dtype])
+    loaded.step.end("w")
+    steps = [[("d", part)] for part in cut(tokens[:split], [29, 2, 50])] + [[("d", [t])] for t in tokens[split:]]
+    check(run_steps(loaded, steps)["d"], want, dtype, what + " (decoded)", limit=SINGLE_LAYER_LIMIT[dtype])
+    return want
+
+
+def moved(want, disk, tensors, tokens, change):
+    """How far the plain model's rows move (in units of their spread) when ``change`` is applied to a copy of its
+    configuration and weights: what a fault of that kind would cost."""
+    other_disk, other = copy.deepcopy(disk), dict(tensors)
+    change(other_disk, other)
+    return spread_error(plain.forward(other_disk, other, tokens), want)
+
+
+WINDOWS = [("rotary", lm.attention(4, 2, 16, 16, rot_dims=8, window=16), 16),        # a page
+           ("rotary", lm.attention(2, 1, 64, 64, window=37, divide=3.0), 37),       # tensor-core head size, no multiple
+           ("rotary", lm.attention(3, 3, 8, 8, window=64), 64),                      # a key tile
+           ("latent", lm.latent(4, 16, 8, 8, 24, 16, window=23), 23),
+           ("latent", lm.latent(2, 32, 64, 16, 64, 24, window=128), 128)]
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("kind,layer,window", WINDOWS)
+def test_keys_just_inside_and_just_outside_a_window(tmp_path, kind, layer, window, dtype):
+    """Sharp scores: a window that is one key short or one key long moves rows by far more than the limit."""
+    folder, disk, tensors = sharp_model(tmp_path, layer, 41, 5.0)
+    tokens = tokens_of(96, 3 * window + 40, 42)
+    want = decode_and_prompt(folder, disk, tensors, tokens, dtype, f"{kind} window {window}", 2 * window + 9)
+
+    def resize(by):
+        def change(d, t):
+            d["layers"][0]["mixer"]["mask"]["size"] = window + by
+        return change
+    for by in (-1, 1):
+        cost = moved(want, disk, tensors, tokens, resize(by))
+        assert (cost > SHOWS[dtype]).sum() >= 5, f"a window off by {by} would not show"
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("heads,groups,dim,buckets,far,every", [(4, 2, 16, 8, 48, 16), (2, 1, 64, 16, 200, 64), (3, 3, 24, 5, 9, 7),
+                                                                 (8, 1, 128, 32, 300, 100)])
+def test_far_keys_distance_buckets_and_the_query_factor(tmp_path, heads, groups, dim, buckets, far, every, dtype):
+    """Every earlier key is visible, the last bucket holds everything beyond ``far``: with sharp scores a change of
+    the last bucket's numbers, of one middle bucket's, or of the query factor's step moves rows well beyond the limit,
+    and the engine agrees with the plain model as it is."""
+    layer = lm.attention_2(heads, groups, dim, dim, buckets, far, temp=(0.6, every))
+    folder, disk, tensors = sharp_model(tmp_path, layer, 43, 3.0)
+    tokens = tokens_of(96, far + 150, 44)
+    want = decode_and_prompt(folder, disk, tensors, tokens, dtype, f"distances up to {far}", far + 60,
+                             max_context=1024, max_batched_tokens=1024)
+
+    def bucket_off(row):
+        def change(d, t):
+            table = t["l0.mix.rel"].copy()
+            table[row] += 2.0
+            t["l0.mix.rel"] = table
+        return change
+
+    def step_off(d, t):
+        d["layers"][0]["mixer"]["q_temp"]["every"] = every + 1
+    for what, change in (("the last bucket", bucket_off(buckets - 1)), ("a middle bucket", bucket_off(buckets // 2 + 1)),
+                         ("the query factor's step", step_off)):
+        cost = moved(want, disk, tensors, tokens, change)
+        assert (cost > SHOWS[dtype]).sum() >= 5, f"a fault in {what} would not show"
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_the_sink_counts_once_in_every_row(tmp_path, dtype):
+    layer = lm.latent(4, 16, 8, 8, 24, 16, window=30)
+    raw = lm.single_layer(layer)
+    bf16 = lm.make_tensors(raw, 45)
+    import torch
+    bf16["l0.mix.sink"] = torch.tensor([5.0, -2.0, 3.5, 8.0], dtype=torch.bfloat16)
+    folder = str(tmp_path / "sink")
+    disk, _ = lm.write_model(folder, raw, 0, tensors=bf16)
+    tensors = plain.as_float64(bf16)
+    tokens = tokens_of(96, 100, 46)
+    want = decode_and_prompt(folder, disk, tensors, tokens, dtype, "sinks", 70)
+
+    def no_sink(d, t):
+        t["l0.mix.sink"] = np.full(4, -1e9)
+    assert (moved(want, disk, tensors, tokens, no_sink) > SHOWS[dtype]).sum() >= 30
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_blended_values_reach_the_cache(tmp_path, dtype):
+    """Two blended layers of different kinds: the later one attends over blended values in prompts and in decoding,
+    also when its request's tokens sit in the middle of a batch."""
+    raw = lm.config(80, 40, [lm.with_mlp(lm.attention(2, 2, 8, 12, rot_dims=4, window=50, v_mix=True), None),
+                             lm.with_mlp(lm.attention_2(4, 2, 8, 12, 6, 30, v_mix=True), 24)], cap=None)
+    folder = str(tmp_path / "blend")
+    import torch
+    bf16 = lm.make_tensors(raw, 47)
+    bf16["l1.mix.vmix"] = torch.tensor(0.875, dtype=torch.bfloat16)
+    disk, _ = lm.write_model(folder, raw, 0, tensors=bf16)
+    tensors = plain.as_float64(bf16)
+    a, b = tokens_of(80, 60, 48), tokens_of(80, 33, 49)
+    want = {"a": plain.forward(disk, tensors, a), "b": plain.forward(disk, tensors, b)}
+    steps = [[("b", b[:5]), ("a", a[:40])]] + [[("b", b[5 + i:6 + i]), ("a", a[40 + i:41 + i])] for i in range(20)] + [[("b", b[25:])]]
+    got = run_steps(load(folder, dtype), steps)
+    for key in want:
+        check(got[key], want[key], dtype, f"request {key} with blended values", limit=SINGLE_LAYER_LIMIT[dtype])
+
+    def unblended(d, t):
+        t["l1.mix.vmix"] = np.float64(0.0)
+    assert (moved(want["a"], disk, tensors, a, unblended) > SHOWS[dtype]).sum() >= 30
+
+
+@pytest.mark.parametrize("dim,vdim", [(8, 5), (32, 32), (40, 72), (72, 16), (128, 64), (200, 8)])
+def test_key_and_value_sizes(tmp_path, dim, vdim):
+    raw = lm.config(70, 40, [lm.with_mlp(lm.attention(2, 1, dim, vdim, rot_dims=dim - dim % 4, window=20), 16),
+                             lm.with_mlp(lm.attention_2(2, 2, dim, vdim, 4, 25), None),
+                             lm.with_mlp(lm.latent(2, dim, 8, vdim, 16, 12), None)])
+    folder = str(tmp_path / "sizes")
+    disk, bf16 = lm.write_model(folder, raw, 50)
+    tensors = plain.as_float64(bf16)
+    tokens = tokens_of(70, 50, 51)
+    want = plain.forward(disk, tensors, tokens)
+    for dtype in ("float32", "bfloat16"):
+        got = run_steps(load(folder, dtype), [[("a", tokens[:30])]] + [[("a", [t])] for t in tokens[30:]])["a"]
+        check(got, want, dtype, f"keys of {dim}, values of {vdim}")
+
+
+# ------------------------------------------------------------------------------------- generation
+@pytest.mark.parametrize("name", ["mixed", "wide"])
+def test_greedy_generation_through_the_engine(models, name):
+    """Prompts of unequal length through ``Engine.generate`` (scheduler, portions, sampler) in float32 against greedy
+    decoding with the plain model."""
+    from celeg_b200 import Engine, EngineOptions
+    folder, raw, tensors = models[name]
+    prompts = [tokens_of(raw["vocab"], n, 50 + n) for n in (5, 41, 18)]
+    new = 12
+    engine = Engine(folder, max_context=128, dtype="float32",
+                    options=EngineOptions(max_active_requests=4, max_batched_tokens=32, page_tokens=16))
+    got = engine.generate(prompts, max_new_tokens=new, temperature=0.0, repetition_penalty=1.0)
+    compared = 0
+    for prompt, generated in zip(prompts, got):
+        assert len(generated) == new
+        sequence = list(prompt)
+        for token in generated:
+            logits = plain.forward(raw, tensors, sequence)[-1]
+            top = np.sort(logits)[-2:]
+            if top[1] - top[0] > 1e-2 * (logits.max() - logits.min()):      # (no near tie in the plain model)
+                assert int(token) == int(np.argmax(logits))
+                compared += 1
+            sequence.append(int(token))
+    assert compared >= 2 * new
+
+
+def test_greedy_generation_in_bfloat16_with_graphs(models):
+    """The serving path (bfloat16, CUDA graphs, run-ahead): the tokens it generates are the plain model's wherever the
+    plain model's best two logits are not close."""
+    from celeg_b200 import Engine, EngineOptions
+    folder, raw, tensors = models["mixed"]
+    prompts = [tokens_of(raw["vocab"], n, 70 + n) for n in (9, 30)]
+    engine = Engine(folder, max_context=128, dtype="bfloat16",
+                    options=EngineOptions(max_active_requests=4, max_batched_tokens=64, page_tokens=16))
+    got = engine.generate(prompts, max_new_tokens=10, temperature=0.0, repetition_penalty=1.0)
+    for prompt, generated in zip(prompts, got):
+        sequence = list(prompt)
+        for token in generated:
+            logits = plain.forward(raw, tensors, sequence)[-1]
+            top = np.sort(logits)[-2:]
+            if top[1] - top[0] > 0.05 * (logits.max() - logits.min()):
+                assert int(token) == int(np.argmax(logits))
+            sequence.append(int(token))
+
+
+def test_many_requests_through_a_small_pool(models):
+    """Nine prompts through two slots and a pool of a few pages: the scheduler queues, admits as slots and pages come
+    free, and every request's tokens are those of greedy decoding alone."""
+    from celeg_b200 import Engine, EngineOptions
+    folder, raw, tensors = models["odd"]
+    prompts = [tokens_of(raw["vocab"], 3 + 5 * n, 200 + n) for n in range(9)]
+    engine = Engine(folder, max_context=96, dtype="float32",
+                    options=EngineOptions(max_active_requests=2, max_batched_tokens=24, page_tokens=16, logical_kv_pages=10))
+    got = engine.generate(prompts, max_new_tokens=6, temperature=0.0, repetition_penalty=1.0)
+    for prompt, generated in zip(prompts, got):
+        sequence = list(prompt)
+        for token in generated:
+            logits = plain.forward(raw, tensors, sequence)[-1]
+            top = np.sort(logits)[-2:]
+            if top[1] - top[0] > 1e-2 * (logits.max() - logits.min()):
+                assert int(token) == int(np.argmax(logits))
+            sequence.append(int(token))
+
+
+def test_command_line_generates_and_dumps_logits(models, tmp_path, capsys):
+    from celeg_b200.cli import main
+    folder, raw, tensors = models["odd"]
+    prompt = tokens_of(raw["vocab"], 12, 90)
+    dump = str(tmp_path / "last.f32")
+    code = main(["--model", folder, "--prompt-ids", ",".join(map(str, prompt)), "--max-new-tokens", "6", "--dtype", "fp32",
+                 "--temperature", "0", "--repetition-penalty", "1.0", "--runtime-tokens", "--dump-logits", dump,
+                 "--context", "128"])
+    assert code == 0
+    captured = capsys.readouterr()
+    sequence = list(prompt)
+    for _ in range(6):
+        sequence.append(int(np.argmax(plain.forward(raw, tensors, sequence)[-1])))
+    assert f"CELEG_GENERATED_TOKEN_IDS=[{','.join(map(str, sequence[len(prompt):]))}]" in captured.out
+    logits = np.fromfile(dump, dtype="<f4").astype(np.float64)
+    assert spread_error(logits[None, :], plain.forward(raw, tensors, prompt)[-1:])[0] < 2e-4
+    assert main(["--model", folder, "--print-config"]) == 0
+    assert '"architecture": "Liverax"' in capsys.readouterr().out
+
+
+# ------------------------------------------------------------------------------- configurations drawn at random
+def random_config(rng):
+    width = int(rng.choice([20, 36, 64, 100, 128]))
+    vocab = int(rng.integers(17, 300))
+    groups, vdim = int(rng.choice([1, 2, 3])), int(rng.choice([4, 9, 16, 64]))     # (one shape for all blended values)
+    layers = []
+    for _ in range(int(rng.integers(1, 6))):
+        kind = rng.integers(0, 3)
+        heads = groups * int(rng.choice([1, 2, 4, 7]))
+        dim = int(rng.choice([4, 8, 12, 32, 64]))
+        window = None if rng.random() < 0.25 else int(rng.choice([1, 3, 16, 33, 64, 100]))
+        if kind == 0:
+            rot = int(rng.choice([2, dim // 2, dim]))
+            layer = lm.attention(heads, groups, dim, vdim, scale=float(rng.choice([dim ** -0.5, 0.125, 0.5])), rot_dims=rot - rot % 2,
+                                 base=float(rng.choice([100.0, 10000.0, 1e6])), divide=None if rng.random() < 0.5 else float(rng.choice([2.0, 8.0])),
+                                 window=window, v_mix=bool(rng.random() < 0.7))
+        elif kind == 1:
+            buckets = int(rng.choice([2, 3, 8, 16, 31]))
+            layer = lm.attention_2(heads, groups, dim, vdim, buckets, buckets // 2 + int(rng.choice([1, 10, 100, 400])),
+                                   scale=float(rng.choice([dim ** -0.5, 0.2])),
+                                   temp=None if rng.random() < 0.3 else (float(rng.choice([0.1, 0.5])), int(rng.choice([1, 8, 50]))),
+                                   v_mix=bool(rng.random() < 0.7))
+        else:
+            layer = lm.latent(int(rng.choice([1, 2, 5, 8])), dim, int(rng.choice([2, 8, 32])), int(rng.choice([4, 9, 32])),
+                              int(rng.choice([8, 24, 64])), int(rng.choice([6, 16, 40])), window=window,
+                              base=float(rng.choice([100.0, 10000.0])))
+        layers.append(lm.with_mlp(layer, None if rng.random() < 0.2 else int(rng.choice([8, 44, 128]))))
+    return lm.config(vocab, width, layers, eps=float(rng.choice([1e-5, 1e-6, 1e-3])),
+                     cap=None if rng.random() < 0.3 else float(rng.choice([10.0, 30.0])))
+
+
+@pytest.mark.parametrize("seed", range(10))
+def test_configurations_drawn_at_random(tmp_path, seed):
+    rng = np.random.default_rng(1000 + seed)
+    raw = random_config(rng)
+    folder = str(tmp_path / "drawn")
+    disk, bf16 = lm.write_model(folder, raw, 2000 + seed)
+    tensors = plain.as_float64(bf16)
+    a, b = tokens_of(raw["vocab"], 120, 3000 + seed), tokens_of(raw["vocab"], 45, 4000 + seed)
+    want = {"a": plain.forward(disk, tensors, a), "b": plain.forward(disk, tensors, b)}
+    steps = [[("a", a[:50]), ("b", b[:2])], [("b", b[2:3]), ("a", a[50:100])]] + [[("a", [t])] for t in a[100:]] + [[("b", b[3:])]]
+    for dtype in ("float32", "bfloat16"):
+        got = run_steps(load(folder, dtype), steps)
+        for key in want:
+            check(got[key], want[key], dtype, f"configuration {seed} request {key}: {raw['layers']}")
+
+
+# ------------------------------------------------------------------------------------- the trace runner
+def replay_steps(requests, seed):
+    """A schedule for up to four live requests: portions of changing size (two tokens too) beside single tokens,
+    requests left out of steps, ended requests followed by new ones."""
+    rng = np.random.default_rng(seed)
+    waiting = list(requests)
+    live, at, steps = [], {}, []
+    while waiting or live:
+        while waiting and len(live) < 4:
+            name = waiting.pop(0)
+            live.append(name)
+            at[name] = 0
+        entries, ended = [], []
+        for name in list(live):
+            tokens = requests[name]
+            left = len(tokens) - at[name]
+            if len(live) > 1 and rng.random() < 0.2:
+                continue                                       # (left out of this step)
+            count = min(left, int(rng.choice([1, 1, 2, 3, 17, 40])))
+            entries.append({"id": name, "tokens": tokens[at[name]:at[name] + count], "want": list(range(count))})
+            at[name] += count
+            if at[name] == len(tokens):
+                ended.append(name)
+                live.remove(name)
+        if entries:
+            steps.append({"step": len(steps), "entries": entries, "end": ended})
+    return steps
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["mixed", "odd"])
+def test_replay_with_pages_and_slots_used_again(models, name, dtype, tmp_path):
+    """Seven requests (640 positions in whole blocks of 64) through the trace runner's step loop with a pool for 448
+    positions, what four live ones can hold at most, and four slots."""
+    import io
+    import json
+    import os
+    from celeg_b200.engine.trace import replay
+    folder, raw, tensors = models[name]
+    lengths = [70, 9, 100, 33, 64, 2, 81]
+    requests = {f"r{i}": tokens_of(raw["vocab"], n, 300 + i) for i, n in enumerate(lengths)}
+    steps = replay_steps(requests, 5)
+    out_dir = str(tmp_path / f"out_{dtype}")
+    done = io.StringIO()
+    text = io.StringIO("".join(json.dumps(step) + "\n" for step in steps))
+    assert replay(folder, dtype, out_dir, 448, text, done, max_requests=4) == 0
+    assert done.getvalue().split() == [w for step in steps for w in ("done", str(step["step"]))]
+    rows = {key: [] for key in requests}
+    for step in steps:
+        data = np.fromfile(os.path.join(out_dir, f"{step['step']}.f32"), dtype="<f4").reshape(-1, raw["vocab"])
+        row = 0
+        for entry in step["entries"]:
+            rows[entry["id"]].append(data[row:row + len(entry["want"])])
+            row += len(entry["want"])
+        assert row == data.shape[0]
+    for key, tokens in requests.items():
+        check(np.concatenate(rows[key]), plain.forward(raw, tensors, tokens), dtype, f"{name} request {key} replayed")
+
+
+def test_the_trace_runner_as_a_program(models, tmp_path):
+    import json
+    import os
+    import subprocess
+    import sys
+    folder, raw, tensors = models["odd"]
+    tokens = tokens_of(raw["vocab"], 21, 400)
+    steps = [{"step": 0, "entries": [{"id": "a", "tokens": tokens[:18], "want": [0, 17]}], "end": []},
+             {"step": 1, "entries": [{"id": "a", "tokens": tokens[18:20], "want": []}], "end": []},
+             {"step": 2, "entries": [{"id": "a", "tokens": tokens[20:], "want": [0]}], "end": ["a"]}]
+    program = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "bin", "trace_run")
+    out_dir = str(tmp_path / "out")
+    result = subprocess.run([program, "--model", folder, "--dtype", "float32", "--out", out_dir, "--max-tokens", "64"],
+                            input="".join(json.dumps(step) + "\n" for step in steps), capture_output=True, text=True,
+                            timeout=600, env=dict(os.environ, PYTHON=sys.executable))
+    assert result.returncode == 0, result.stderr[-2000:]
+    assert [line for line in result.stdout.split("\n") if line.startswith("done")] == ["done 0", "done 1", "done 2"]
+    assert not os.path.exists(os.path.join(out_dir, "1.f32"))
+    want = plain.forward(raw, tensors, tokens)
+    got = np.concatenate([np.fromfile(os.path.join(out_dir, f"{n}.f32"), dtype="<f4").reshape(-1, raw["vocab"]) for n in (0, 2)])
+    check(got, want[[0, 17, 20]], "float32", "the program's logits")
