@@ -8,7 +8,7 @@ batch 1 and 64. Prints ONE JSON line.
                   [--prefill-tokens T] [--chunk C] [--kernel-times] [--no-cuda-graph]      one phase, a short record
   python bench.py --workload lfm2-700m|lfm2-350m [--requests N] [--new-tokens N] [--max-batched-tokens N]
                   [--prefill-chunk N] [--kernel-times]       a scheduler workload through Engine.submit/step/poll
-  python bench.py --design ramosun|kedesun|naselorn [--design-size w1024|w2048] [--kernel-times]
+  python bench.py --design ramosun|kedesun|naselorn|liverax [--design-size w1024|w2048] [--kernel-times]
                   the Ramosun design beside the closest LFM2 model at equal size: prefill of 2,048 tokens, decode at batch 8
 
 A "step" is one decode step of the whole batch. ``value`` is timed on the device (CUDA events
@@ -198,7 +198,8 @@ class KernelTimer:
              "depth_average", "latent_prepare", "head_project", "head_gate", "moe_route", "moe_group", "moe_gather_rows",
              "expert_product", "expert_product_tcgen05", "expert_rows", "moe_combine", "retention_segmented",
              "retention_decode_raw", "activation_columns", "bias_store_kv", "scaled_sum", "glu", "lru_prepare",
-             "block_diagonal_product", "lru_scan", "lru_decode")
+             "block_diagonal_product", "lru_scan", "lru_decode", "add_layernorm", "qkv_prepare", "rmsnorm_strided",
+             "sigmoid_gate")
 
     def __init__(self):
         self.pairs = []
@@ -519,6 +520,37 @@ def naselorn_config(width: int, vocab: int) -> dict:
             "embedding": {"scale": float(width) ** 0.5}, "layers": run + run, "max_context": 8192}
 
 
+def liverax_config(width: int, vocab: int) -> dict:
+    """Eight layers, all softmax attention: rotary attention under a window of 1,024 positions, latent attention under
+    the same window with sinks, rotary attention, attention with distance biases over every earlier position, twice.
+    Query heads of 64 on a quarter as many key heads, values blended across the six layers that keep keys and
+    values; the latent mixer has Kedesun's sizes (heads of 64 + 64 over a cached vector of 192 + 64) behind a query
+    latent of three eighths of the width; thirty-two distance buckets up to 2,048 positions; a gated feed-forward of
+    8/3 width."""
+    heads = width // 64
+    ff = {"kind": "dense", "ff": (8 * width // 3 + 127) // 128 * 128}
+    rotary = {"type": "attention", "mlp": ff, "mixer": {
+        "heads": heads, "kv_heads": heads // 4, "dim": 64, "vdim": 64, "scale": 0.125, "mask": {"size": 1024},
+        "rot": {"base": 1000000.0, "dims": 64, "scaling": {"factor": 2.0}}, "v_mix": True}}
+    latent = {"type": "latent_attention", "mlp": ff, "mixer": {
+        "heads": width // 128, "dim": 64, "rot_dim": 64, "vdim": 64, "kv_rank": 192, "q_rank": 3 * width // 8,
+        "scale": 128 ** -0.5, "mask": {"size": 1024}, "rot": {"base": 10000.0, "dims": 64}}}
+    distance = {"type": "attention_2", "mlp": ff, "mixer": {
+        "heads": heads, "kv_heads": heads // 4, "dim": 64, "vdim": 64, "scale": 0.125, "bias_max": 2048,
+        "q_temp": {"coef": 0.1, "every": 512}, "v_mix": True}}
+    run = [rotary, latent, rotary, distance]
+    return {"architecture": "Liverax", "vocab": vocab, "width": width, "norm": {"eps": 1e-5}, "logit_softcap": 30.0,
+            "layers": run + run, "distance_buckets": [0, 0, 0, 32] * 2, "max_context": 8192}
+
+
+def lfm2_attention_only(width: int, vocab: int) -> dict:
+    """The LFM2 relative with attention in all eight blocks: the existing model closest to a design whose mixers are all
+    softmax attention (pre-norm blocks, grouped queries, rotation of halves, a gated feed-forward)."""
+    raw = lfm2_relative(width, vocab)
+    raw["layer_types"] = ["full_attention"] * 8
+    return raw
+
+
 def lfm2_relative(width: int, vocab: int) -> dict:
     raw = dict(LFM2_1P2B)
     # eight blocks like Ramosun's run order; a SwiGLU of 8/3 width has the parameters of a dense feed-forward of 4 width
@@ -547,6 +579,9 @@ def run_design(args) -> dict:
         elif args.design == "naselorn":  # beside Kedesun, whose layers it resembles most (fixed decays, experts)
             models = (("naselorn", naselorn_config(width, vocab)), ("kedesun", kedesun_config(width, vocab)),
                       ("lfm2", lfm2_relative(width, vocab)))
+        elif args.design == "liverax":   # beside LFM2 with attention in every block, and Kedesun for the latent mixer
+            models = (("liverax", liverax_config(width, vocab)), ("lfm2_attention", lfm2_attention_only(width, vocab)),
+                      ("kedesun", kedesun_config(width, vocab)))
         else:
             models = (("ramosun", ramosun_config(width, vocab)), ("lfm2", lfm2_relative(width, vocab)))
         for name, raw in models:
@@ -828,7 +863,7 @@ def main() -> int:
     parser.add_argument("--new-tokens", type=int, default=0, help="--workload: tokens to generate per request")
     parser.add_argument("--max-batched-tokens", type=int, default=0, help="--workload: token budget of a step")
     parser.add_argument("--prefill-chunk", type=int, default=0, help="--workload: longest prompt portion")
-    parser.add_argument("--design", default=None, choices=["ramosun", "kedesun", "naselorn"],
+    parser.add_argument("--design", default=None, choices=["ramosun", "kedesun", "naselorn", "liverax"],
                         help="prefill and decode of that design beside the closest LFM2 model at equal size")
     parser.add_argument("--design-size", default=None, choices=sorted(DESIGN_SIZES), help="--design: one size only")
     parser.add_argument("--no-warmup-run", action="store_true",
