@@ -38,17 +38,19 @@ struct QkvPrepareArgs {
 template <typename A>
 __global__ void qkv_prepare_kernel(const QkvPrepareArgs p) {
     __shared__ float scratch[33];
-    extern __shared__ float row_s[];          // q | k as float32, then cos | sin of the token's angles
+    extern __shared__ __align__(16) float row_s[];       // q | k as float32, then cos | sin of the token's angles
     chain_release();
     chain_wait();
     const int t = blockIdx.x;
-    const int q_width = p.q_heads * p.head_dim, k_width = p.kv_heads * p.head_dim, v_width = p.kv_heads * p.value_dim;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
+    const int q_width = p.q_heads * p.head_dim, k_width = p.kv_heads * p.head_dim;
+    const int qk_width = q_width + k_width;
     const int pos = p.positions[t];
     const int page = p.block_table[(size_t)p.token_span[t] * p.table_stride + pos / p.page_tokens];
     if (page < 0 && threadIdx.x == 0) atomicExch(p.error_flag, 2);
     const float* row = p.proj + (size_t)t * p.proj_stride;
     float* qk = row_s;
-    float* turn = row_s + q_width + k_width;
+    float* turn = row_s + ((qk_width + 3) & ~3);
     const int half = p.frequencies ? p.rotary_dim >> 1 : 0;
     for (int i = threadIdx.x; i < half; i += blockDim.x) {
         float s, c;
@@ -56,11 +58,29 @@ __global__ void qkv_prepare_kernel(const QkvPrepareArgs p) {
         turn[i] = c;
         turn[half + i] = s;
     }
+    // q and k with their biases into shared memory (four at a time where the rows allow it), and their squares
     float q_squares = 0.0f, k_squares = 0.0f;
-    for (int i = threadIdx.x; i < q_width + k_width; i += blockDim.x) {
-        const float x = row[i] + (p.bias ? p.bias[i] : 0.0f);
-        qk[i] = x;
-        if (i < q_width) q_squares += x * x; else k_squares += x * x;
+    const bool by_four = (qk_width & 3) == 0 && (q_width & 3) == 0 && (p.proj_stride & 3) == 0 &&
+                         ((size_t)p.proj & 15) == 0 && ((size_t)p.bias & 15) == 0;
+    if (by_four) {
+        const float4* row4 = reinterpret_cast<const float4*>(row);
+        const float4* bias4 = reinterpret_cast<const float4*>(p.bias);
+        for (int i = threadIdx.x; i < (qk_width >> 2); i += blockDim.x) {
+            float4 x = row4[i];
+            if (bias4) {
+                const float4 b = __ldg(bias4 + i);
+                x.x += b.x; x.y += b.y; x.z += b.z; x.w += b.w;
+            }
+            reinterpret_cast<float4*>(qk)[i] = x;
+            const float squares = x.x * x.x + x.y * x.y + x.z * x.z + x.w * x.w;
+            if (4 * i < q_width) q_squares += squares; else k_squares += squares;
+        }
+    } else {
+        for (int i = threadIdx.x; i < qk_width; i += blockDim.x) {
+            const float x = row[i] + (p.bias ? p.bias[i] : 0.0f);
+            qk[i] = x;
+            if (i < q_width) q_squares += x * x; else k_squares += x * x;
+        }
     }
     float q_factor = 1.0f, k_factor = 1.0f;
     if (p.q_norm_w) {
@@ -68,54 +88,52 @@ __global__ void qkv_prepare_kernel(const QkvPrepareArgs p) {
         k_factor = 1.0f / sqrtf(block_sum(k_squares, scratch) / (float)k_width + p.norm_eps);
     }
     __syncthreads();
-    if (p.q_norm_w) {
-        for (int i = threadIdx.x; i < q_width + k_width; i += blockDim.x)
-            qk[i] = i < q_width ? qk[i] * q_factor * p.q_norm_w[i] : qk[i] * k_factor * p.k_norm_w[i - q_width];
-        __syncthreads();
-    }
-    if (half > 0) {
-        const int heads = p.q_heads + p.kv_heads;             // k heads follow the q heads at the same head size
-        for (int unit = threadIdx.x; unit < heads * half; unit += blockDim.x) {
-            const int h = unit / half, i = unit - h * half;
-            float* head = qk + (size_t)h * p.head_dim;
-            const float u = head[i], v = head[i + half];
-            head[i] = u * turn[i] - v * turn[half + i];
-            head[i + half] = v * turn[i] + u * turn[half + i];
-        }
-        __syncthreads();
-    }
     const float temperature = p.temp_every > 0
         ? 1.0f + p.temp_coef * logf((float)((pos + 1) / p.temp_every + 1)) : 1.0f;
     A* q_row = static_cast<A*>(p.q_out) + (size_t)t * p.q_stride;
-    A* k_cache = static_cast<A*>(p.k_cache);
-    A* v_cache = static_cast<A*>(p.v_cache);
     const long long in_page = pos % p.page_tokens;
-    const int q_store = p.q_heads * p.key_store, k_store = p.kv_heads * p.key_store, v_store = p.kv_heads * p.value_store;
-    for (int i = threadIdx.x; i < q_store + k_store + v_store; i += blockDim.x) {
-        if (i < q_store) {
-            const int head = i / p.key_store, e = i % p.key_store;
-            q_row[i] = from_float<A>(e < p.head_dim ? qk[head * p.head_dim + e] * temperature : 0.0f);
-        } else if (i < q_store + k_store) {
-            if (page < 0) continue;
-            const int j = i - q_store, head = j / p.key_store, e = j % p.key_store;
-            k_cache[(long long)page * p.page_stride + ((long long)head * p.page_tokens + in_page) * p.key_store + e] =
-                from_float<A>(e < p.head_dim ? qk[q_width + head * p.head_dim + e] : 0.0f);
-        } else {
-            const int j = i - q_store - k_store, head = j / p.value_store, e = j % p.value_store;
+    // a warp a head: norm scale, rotation, the query factor and the store in one pass over shared memory
+    for (int unit = warp; unit < p.q_heads + p.kv_heads; unit += warps) {
+        const bool is_q = unit < p.q_heads;
+        if (!is_q && page < 0) continue;
+        const float* head = qk + (size_t)unit * p.head_dim;
+        const float* weight = !p.q_norm_w ? nullptr
+                              : (is_q ? p.q_norm_w + (size_t)unit * p.head_dim
+                                      : p.k_norm_w + (size_t)(unit - p.q_heads) * p.head_dim);
+        const float factor = is_q ? q_factor : k_factor;
+        const float after = is_q ? temperature : 1.0f;
+        A* dst = is_q ? q_row + (size_t)unit * p.key_store
+                      : static_cast<A*>(p.k_cache) + (long long)page * p.page_stride +
+                            ((long long)(unit - p.q_heads) * p.page_tokens + in_page) * p.key_store;
+        for (int i = lane; i < half; i += 32) {
+            float u = head[i] * factor, v = head[i + half] * factor;
+            if (weight) {
+                u *= weight[i];
+                v *= weight[i + half];
+            }
+            dst[i] = from_float<A>((u * turn[i] - v * turn[half + i]) * after);
+            dst[i + half] = from_float<A>((v * turn[i] + u * turn[half + i]) * after);
+        }
+        for (int e = 2 * half + lane; e < p.head_dim; e += 32)
+            dst[e] = from_float<A>(head[e] * factor * (weight ? weight[e] : 1.0f) * after);
+        for (int e = p.head_dim + lane; e < p.key_store; e += 32) dst[e] = from_float<A>(0.0f);
+    }
+    for (int unit = warp; unit < p.kv_heads; unit += warps) {
+        A* dst = page < 0 ? nullptr
+                          : static_cast<A*>(p.v_cache) + (long long)page * p.value_page_stride +
+                                ((long long)unit * p.page_tokens + in_page) * p.value_store;
+        for (int e = lane; e < p.value_store; e += 32) {
             float v = 0.0f;
             if (e < p.value_dim) {
-                const int column = head * p.value_dim + e;
-                const int src = q_width + k_width + column;
+                const int column = unit * p.value_dim + e;
+                const int src = qk_width + column;
                 v = row[src] + (p.bias ? p.bias[src] : 0.0f);
                 if (p.blend == 1) p.first_values[(size_t)t * p.first_stride + column] = v;
                 if (p.blend == 2) v = (1.0f - p.lam) * v + p.lam * p.first_values[(size_t)t * p.first_stride + column];
             }
-            if (page >= 0)
-                v_cache[(long long)page * p.value_page_stride +
-                        ((long long)head * p.page_tokens + in_page) * p.value_store + e] = from_float<A>(v);
+            if (dst) dst[e] = from_float<A>(v);
         }
     }
-    (void)v_width;
 }
 
 }  // namespace celeg_b200
@@ -144,7 +162,7 @@ CELEG_API int celeg_qkv_prepare(const float* proj, int proj_stride, const float*
                   "qkv_prepare: blend %d without a place for the first values (stride %d)", blend, first_stride);
     CELEG_REQUIRE(act_dtype == kFloat32 || act_dtype == kBFloat16, "qkv_prepare: unknown dtype code %d", act_dtype);
     if (tokens == 0) return 0;
-    const size_t smem = ((size_t)(q_heads + kv_heads) * head_dim + (frequencies ? rotary_dim : 0)) * sizeof(float);
+    const size_t smem = ((((size_t)(q_heads + kv_heads) * head_dim + 3) & ~(size_t)3) + (frequencies ? rotary_dim : 0)) * sizeof(float);
     CELEG_REQUIRE(smem <= 200 * 1024, "qkv_prepare: a row of %zu bytes exceeds a block's shared memory", smem);
     const QkvPrepareArgs args = {proj, proj_stride, bias, q_norm_w, k_norm_w, norm_eps, frequencies, rotary_dim,
                                  temp_coef, temp_every, blend, lam, first_values, first_stride, q_out, q_stride,

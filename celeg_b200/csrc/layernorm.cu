@@ -61,6 +61,81 @@ __global__ void add_layernorm_kernel(float* residual, const A* delta, const floa
     }
 }
 
+// Widths that are a multiple of 4 with 16-byte aligned rows: four elements a load, a thread's elements in registers
+// between the passes (the stream is read once).
+template <typename A, int kPerThread>
+__global__ void add_layernorm_vec4_kernel(float* residual, const A* delta, const float* __restrict__ weight,
+                                          const float* __restrict__ bias, A* out, const int* rows, int width, float eps,
+                                          int write_residual) {
+    __shared__ float scratch[33];
+    chain_release();
+    chain_wait();
+    const int i = blockIdx.x;
+    const int r = rows ? rows[i] : i;
+    float4* res = reinterpret_cast<float4*>(residual + (size_t)r * width);
+    const int quads = width >> 2;
+    float4 x[kPerThread];
+    float sum = 0.0f;
+#pragma unroll
+    for (int u = 0; u < kPerThread; ++u) {
+        const int q = threadIdx.x + u * blockDim.x;
+        float4 v = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        if (q < quads) {
+            v = res[q];
+            if (delta) {
+                const A* d = delta + (size_t)r * width + 4 * q;
+                if (sizeof(A) == 2) {
+                    const uint2 raw = *reinterpret_cast<const uint2*>(d);
+                    const float2 lo = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.x));
+                    const float2 hi = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.y));
+                    v.x += lo.x; v.y += lo.y; v.z += hi.x; v.w += hi.y;
+                } else {
+                    const float4 dv = *reinterpret_cast<const float4*>(d);
+                    v.x += dv.x; v.y += dv.y; v.z += dv.z; v.w += dv.w;
+                }
+                if (write_residual) res[q] = v;
+            }
+        }
+        x[u] = v;
+        sum += (v.x + v.y) + (v.z + v.w);
+    }
+    const float mean = block_sum(sum, scratch) / (float)width;
+    float squares = 0.0f;
+#pragma unroll
+    for (int u = 0; u < kPerThread; ++u) {
+        const int q = threadIdx.x + u * blockDim.x;
+        if (q < quads) {
+            float4 v = x[u];
+            v.x -= mean; v.y -= mean; v.z -= mean; v.w -= mean;
+            x[u] = v;
+            squares += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+        }
+    }
+    const float inv = 1.0f / sqrtf(block_sum(squares, scratch) / (float)width + eps);
+#pragma unroll
+    for (int u = 0; u < kPerThread; ++u) {
+        const int q = threadIdx.x + u * blockDim.x;
+        if (q < quads) {
+            const float4 w = __ldg(reinterpret_cast<const float4*>(weight) + q);
+            const float4 b = bias ? __ldg(reinterpret_cast<const float4*>(bias) + q) : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+            const float4 v = x[u];
+            const float4 y = make_float4(v.x * inv * w.x + b.x, v.y * inv * w.y + b.y, v.z * inv * w.z + b.z,
+                                         v.w * inv * w.w + b.w);
+            A* dst = out + (size_t)i * width + 4 * q;
+            if (sizeof(A) == 2) {
+                const __nv_bfloat162 lo = __floats2bfloat162_rn(y.x, y.y);
+                const __nv_bfloat162 hi = __floats2bfloat162_rn(y.z, y.w);
+                uint2 raw;
+                raw.x = *reinterpret_cast<const unsigned*>(&lo);
+                raw.y = *reinterpret_cast<const unsigned*>(&hi);
+                *reinterpret_cast<uint2*>(dst) = raw;
+            } else {
+                *reinterpret_cast<float4*>(dst) = y;
+            }
+        }
+    }
+}
+
 // rows wider than a block's registers hold: three passes over memory
 template <typename A>
 __global__ void add_layernorm_wide_kernel(float* residual, const A* delta, const float* __restrict__ weight,
@@ -125,7 +200,15 @@ template <typename A>
 static void launch_layernorm(float* residual, const void* delta, const float* weight, const float* bias, void* out,
                              const int* rows, int n_rows, int width, float eps, int write_residual, cudaStream_t stream) {
     constexpr int kPerThread = 8;
-    if (width <= 1024 * kPerThread) {
+    constexpr int kQuads = 4;
+    const bool aligned = (((size_t)residual | (size_t)delta | (size_t)weight | (size_t)bias | (size_t)out) & 15) == 0;
+    if (width % 4 == 0 && width <= 1024 * 4 * kQuads && aligned) {
+        int threads = (width / 4 + kQuads - 1) / kQuads;
+        threads = (threads + 31) / 32 * 32;
+        if (threads < 64) threads = 64;
+        launch_chained_class(kChainNorm, add_layernorm_vec4_kernel<A, kQuads>, n_rows, threads, 0, stream, residual,
+                             (const A*)delta, weight, bias, (A*)out, rows, width, eps, write_residual);
+    } else if (width <= 1024 * kPerThread) {
         int threads = (width + kPerThread - 1) / kPerThread;
         threads = (threads + 31) / 32 * 32;
         if (threads < 64) threads = 64;
