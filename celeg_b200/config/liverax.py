@@ -16,7 +16,17 @@ from dataclasses import dataclass
 from typing import Any, Dict, Mapping, Optional, Tuple
 
 from .errors import ConfigError
-from .ramosun import DEFAULT_MAX_CONTEXT, _need, _positive_int
+from .ramosun import DEFAULT_MAX_CONTEXT, _need
+
+
+def _positive_int(mapping: Mapping[str, Any], key: str, where: str) -> int:
+    """A count; a JSON writer may have left a whole number as 240.0."""
+    value = _need(mapping, key, where)
+    if isinstance(value, float) and value.is_integer():
+        value = int(value)
+    if isinstance(value, bool) or not isinstance(value, int) or value <= 0:
+        raise ConfigError(f"{where}: '{key}' must be a positive integer, got {value!r}")
+    return value
 
 ATTENTION, DISTANCE_ATTENTION, LATENT_ATTENTION = "attention", "attention_2", "latent_attention"
 LAYER_TYPES = (ATTENTION, DISTANCE_ATTENTION, LATENT_ATTENTION)

@@ -38,49 +38,71 @@ struct QkvPrepareArgs {
 template <typename A>
 __global__ void qkv_prepare_kernel(const QkvPrepareArgs p) {
     __shared__ float scratch[33];
-    extern __shared__ __align__(16) float row_s[];       // q | k as float32, then cos | sin of the token's angles
+    extern __shared__ __align__(16) float row_s[];       // q | k | v as float32, the first values, cos | sin of the angles
     chain_release();
     chain_wait();
     const int t = blockIdx.x;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
     const int q_width = p.q_heads * p.head_dim, k_width = p.kv_heads * p.head_dim;
     const int qk_width = q_width + k_width;
+    // (the token's position and span are asked for first and used last: the row's loads do not wait for them, and
+    // the page's number, which hangs on both, is under way while the angles are made)
     const int pos = p.positions[t];
-    const int page = p.block_table[(size_t)p.token_span[t] * p.table_stride + pos / p.page_tokens];
-    if (page < 0 && threadIdx.x == 0) atomicExch(p.error_flag, 2);
+    const int span = p.token_span[t];
     const float* row = p.proj + (size_t)t * p.proj_stride;
-    float* qk = row_s;
-    float* turn = row_s + ((qk_width + 3) & ~3);
+    const int v_width = p.kv_heads * p.value_dim;
+    const int row_width = qk_width + v_width;
+    float* qk = row_s;                                    // q | k | v, biases added
+    float* first_s = row_s + ((row_width + 3) & ~3);      // the first values of this token (blend 2)
+    float* turn = first_s + (p.blend == 2 ? ((v_width + 3) & ~3) : 0);
     const int half = p.frequencies ? p.rotary_dim >> 1 : 0;
+    const float* first_row = p.blend == 2 ? p.first_values + (size_t)t * p.first_stride : nullptr;
+    // The row with its biases into shared memory, and the squares of q and of k. Four at a time where the rows allow
+    // it, and then every load of a thread is under way before the first is used: a block's time is the time of its
+    // chains of dependent loads.
+    float q_squares = 0.0f, k_squares = 0.0f;
+    const bool by_four = ((row_width | qk_width | q_width | p.proj_stride) & 3) == 0 && ((size_t)p.proj & 15) == 0 &&
+                         ((size_t)p.bias & 15) == 0;
+    if (by_four) {
+        constexpr int kAhead = 4;
+        const float4* row4 = reinterpret_cast<const float4*>(row);
+        const float4* bias4 = reinterpret_cast<const float4*>(p.bias);
+        const int quads = row_width >> 2;
+        for (int base = threadIdx.x; base < quads; base += kAhead * blockDim.x) {
+            float4 x[kAhead];
+#pragma unroll
+            for (int u = 0; u < kAhead; ++u) {
+                const int i = base + u * blockDim.x;
+                x[u] = i < quads ? row4[i] : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+            }
+#pragma unroll
+            for (int u = 0; u < kAhead; ++u) {
+                const int i = base + u * blockDim.x;
+                if (i >= quads) continue;
+                if (bias4) {
+                    const float4 b = __ldg(bias4 + i);
+                    x[u].x += b.x; x[u].y += b.y; x[u].z += b.z; x[u].w += b.w;
+                }
+                reinterpret_cast<float4*>(qk)[i] = x[u];
+                const float squares = x[u].x * x[u].x + x[u].y * x[u].y + x[u].z * x[u].z + x[u].w * x[u].w;
+                if (4 * i < q_width) q_squares += squares; else if (4 * i < qk_width) k_squares += squares;
+            }
+        }
+    } else {
+        for (int i = threadIdx.x; i < row_width; i += blockDim.x) {
+            const float x = row[i] + (p.bias ? p.bias[i] : 0.0f);
+            qk[i] = x;
+            if (i < q_width) q_squares += x * x; else if (i < qk_width) k_squares += x * x;
+        }
+    }
+    if (first_row)
+        for (int i = threadIdx.x; i < v_width; i += blockDim.x) first_s[i] = first_row[i];
+    const int page = p.block_table[(size_t)span * p.table_stride + pos / p.page_tokens];
     for (int i = threadIdx.x; i < half; i += blockDim.x) {
         float s, c;
         sincosf((float)pos * p.frequencies[i], &s, &c);
         turn[i] = c;
         turn[half + i] = s;
-    }
-    // q and k with their biases into shared memory (four at a time where the rows allow it), and their squares
-    float q_squares = 0.0f, k_squares = 0.0f;
-    const bool by_four = (qk_width & 3) == 0 && (q_width & 3) == 0 && (p.proj_stride & 3) == 0 &&
-                         ((size_t)p.proj & 15) == 0 && ((size_t)p.bias & 15) == 0;
-    if (by_four) {
-        const float4* row4 = reinterpret_cast<const float4*>(row);
-        const float4* bias4 = reinterpret_cast<const float4*>(p.bias);
-        for (int i = threadIdx.x; i < (qk_width >> 2); i += blockDim.x) {
-            float4 x = row4[i];
-            if (bias4) {
-                const float4 b = __ldg(bias4 + i);
-                x.x += b.x; x.y += b.y; x.z += b.z; x.w += b.w;
-            }
-            reinterpret_cast<float4*>(qk)[i] = x;
-            const float squares = x.x * x.x + x.y * x.y + x.z * x.z + x.w * x.w;
-            if (4 * i < q_width) q_squares += squares; else k_squares += squares;
-        }
-    } else {
-        for (int i = threadIdx.x; i < qk_width; i += blockDim.x) {
-            const float x = row[i] + (p.bias ? p.bias[i] : 0.0f);
-            qk[i] = x;
-            if (i < q_width) q_squares += x * x; else k_squares += x * x;
-        }
     }
     float q_factor = 1.0f, k_factor = 1.0f;
     if (p.q_norm_w) {
@@ -92,6 +114,7 @@ __global__ void qkv_prepare_kernel(const QkvPrepareArgs p) {
         ? 1.0f + p.temp_coef * logf((float)((pos + 1) / p.temp_every + 1)) : 1.0f;
     A* q_row = static_cast<A*>(p.q_out) + (size_t)t * p.q_stride;
     const long long in_page = pos % p.page_tokens;
+    if (page < 0 && threadIdx.x == 0) atomicExch(p.error_flag, 2);
     // a warp a head: norm scale, rotation, the query factor and the store in one pass over shared memory
     for (int unit = warp; unit < p.q_heads + p.kv_heads; unit += warps) {
         const bool is_q = unit < p.q_heads;
@@ -126,10 +149,9 @@ __global__ void qkv_prepare_kernel(const QkvPrepareArgs p) {
             float v = 0.0f;
             if (e < p.value_dim) {
                 const int column = unit * p.value_dim + e;
-                const int src = qk_width + column;
-                v = row[src] + (p.bias ? p.bias[src] : 0.0f);
+                v = qk[qk_width + column];
                 if (p.blend == 1) p.first_values[(size_t)t * p.first_stride + column] = v;
-                if (p.blend == 2) v = (1.0f - p.lam) * v + p.lam * p.first_values[(size_t)t * p.first_stride + column];
+                if (p.blend == 2) v = (1.0f - p.lam) * v + p.lam * first_s[column];
             }
             if (dst) dst[e] = from_float<A>(v);
         }
@@ -162,7 +184,9 @@ CELEG_API int celeg_qkv_prepare(const float* proj, int proj_stride, const float*
                   "qkv_prepare: blend %d without a place for the first values (stride %d)", blend, first_stride);
     CELEG_REQUIRE(act_dtype == kFloat32 || act_dtype == kBFloat16, "qkv_prepare: unknown dtype code %d", act_dtype);
     if (tokens == 0) return 0;
-    const size_t smem = ((((size_t)(q_heads + kv_heads) * head_dim + 3) & ~(size_t)3) + (frequencies ? rotary_dim : 0)) * sizeof(float);
+    const size_t row_floats = ((size_t)(q_heads + kv_heads) * head_dim + (size_t)kv_heads * value_dim + 3) & ~(size_t)3;
+    const size_t first_floats = blend == 2 ? (((size_t)kv_heads * value_dim + 3) & ~(size_t)3) : 0;
+    const size_t smem = (row_floats + first_floats + (frequencies ? rotary_dim : 0)) * sizeof(float);
     CELEG_REQUIRE(smem <= 200 * 1024, "qkv_prepare: a row of %zu bytes exceeds a block's shared memory", smem);
     const QkvPrepareArgs args = {proj, proj_stride, bias, q_norm_w, k_norm_w, norm_eps, frequencies, rotary_dim,
                                  temp_coef, temp_every, blend, lam, first_values, first_stride, q_out, q_stride,

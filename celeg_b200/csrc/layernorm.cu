@@ -196,6 +196,28 @@ __global__ void sigmoid_gate_kernel(A* values, long long stride, const G* gate, 
     *cell = from_float<A>(to_float(*cell) * g);
 }
 
+// four neighbours a thread (rows whose widths and strides are multiples of four, 16-byte aligned gate rows)
+template <typename A, typename G>
+__global__ void sigmoid_gate_vec4_kernel(A* values, long long stride, const G* gate, long long gate_stride, int tokens,
+                                         int width) {
+    chain_release();
+    chain_wait();
+    const int quads = width >> 2;
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= (long long)tokens * quads) return;
+    const int t = (int)(i / quads), c = 4 * (int)(i % quads);
+    A* cell = values + (size_t)t * stride + c;
+    const G* g = gate + (size_t)t * gate_stride + c;
+    float v[4], z[4];
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+        v[e] = to_float(cell[e]);
+        z[e] = to_float(g[e]);
+    }
+#pragma unroll
+    for (int e = 0; e < 4; ++e) cell[e] = from_float<A>(v[e] / (1.0f + __expf(-z[e])));
+}
+
 template <typename A>
 static void launch_layernorm(float* residual, const void* delta, const float* weight, const float* bias, void* out,
                              const int* rows, int n_rows, int width, float eps, int write_residual, cudaStream_t stream) {
@@ -266,6 +288,12 @@ CELEG_API int celeg_sigmoid_gate(void* values, long long stride, const void* gat
     CELEG_REQUIRE((act_dtype == kFloat32 || act_dtype == kBFloat16) && (gate_dtype == kFloat32 || gate_dtype == act_dtype),
                   "sigmoid_gate: dtype codes %d / %d", act_dtype, gate_dtype);
     if (tokens == 0) return 0;
+    if (act_dtype == kBFloat16 && gate_dtype == kFloat32 && width % 4 == 0 && stride % 4 == 0 && gate_stride % 4 == 0) {
+        const unsigned quad_blocks = (unsigned)(((long long)tokens * (width / 4) + 255) / 256);
+        launch_chained(sigmoid_gate_vec4_kernel<__nv_bfloat16, float>, quad_blocks, 256, 0, stream, (__nv_bfloat16*)values,
+                       stride, (const float*)gate, gate_stride, tokens, width);
+        return check_launch("sigmoid_gate");
+    }
     const unsigned blocks = (unsigned)(((long long)tokens * width + 255) / 256);
     if (act_dtype == kFloat32)
         launch_chained(sigmoid_gate_kernel<float, float>, blocks, 256, 0, stream, (float*)values, stride,
