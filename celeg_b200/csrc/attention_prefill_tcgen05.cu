@@ -271,9 +271,16 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
                 if (p.distance_bias) {
                     const float* bias = p.distance_bias + (size_t)h * (p.distance_last + 1);
                     const int back = qpos - key_base;               // key key_base + j lies back - j positions back
+                    if (back - (kFaN - 1) >= p.distance_last) {
+                        // every key of the block is as far as the table goes: one number for the whole row
+                        const float far = __ldg(bias + p.distance_last) * p.bias_factor;
 #pragma unroll
-                    for (int j = 0; j < kFaN; ++j)
-                        sc[j] = fmaf(__ldg(bias + max(0, min(back - j, p.distance_last))), p.bias_factor, sc[j]);
+                        for (int j = 0; j < kFaN; ++j) sc[j] += far;
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < kFaN; ++j)
+                            sc[j] = fmaf(__ldg(bias + max(0, min(back - j, p.distance_last))), p.bias_factor, sc[j]);
+                    }
                 }
                 if (!full) {
                     // keys key_base + [lo, hi] are the ones this row sees
