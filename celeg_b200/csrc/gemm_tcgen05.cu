@@ -144,12 +144,21 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             if (EPI == kTcSwiGlu) {
                 float u[32];
                 tmem_load_32(tmem_base + ((unsigned)(warp * 32) << 16) + (unsigned)(BN / 2 + c0), u);
+                if (p.activation == kSilu) {
 #pragma unroll
-                for (int i = 0; i < 32; ++i) {
-                    // gate and up as a plain product would store them (one rounding each)
-                    const float g = __bfloat162float(__float2bfloat16_rn(v[i]));
-                    const float up = __bfloat162float(__float2bfloat16_rn(u[i]));
-                    v[i] = g / (1.0f + expf(-g)) * up;
+                    for (int i = 0; i < 32; ++i) {
+                        // gate and up as a plain product would store them (one rounding each)
+                        const float g = __bfloat162float(__float2bfloat16_rn(v[i]));
+                        const float up = __bfloat162float(__float2bfloat16_rn(u[i]));
+                        v[i] = g / (1.0f + expf(-g)) * up;
+                    }
+                } else {                          // another function of the gate (a code of activate())
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) {
+                        const float g = __bfloat162float(__float2bfloat16_rn(v[i]));
+                        const float up = __bfloat162float(__float2bfloat16_rn(u[i]));
+                        v[i] = activate(g, p.activation) * up;
+                    }
                 }
             }
             if (EPI == kTcActivation) {
@@ -360,11 +369,20 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const 
                 if (EPI == kTcSwiGlu) {
                     float u[32];
                     tmem_load_32(lane_base + (unsigned)(BN / 2 + c0), u);
+                    if (p.activation == kSilu) {
 #pragma unroll
-                    for (int i = 0; i < 32; ++i) {
-                        const float g = __bfloat162float(__float2bfloat16_rn(v[i]));
-                        const float up = __bfloat162float(__float2bfloat16_rn(u[i]));
-                        v[i] = g / (1.0f + expf(-g)) * up;
+                        for (int i = 0; i < 32; ++i) {
+                            const float g = __bfloat162float(__float2bfloat16_rn(v[i]));
+                            const float up = __bfloat162float(__float2bfloat16_rn(u[i]));
+                            v[i] = g / (1.0f + expf(-g)) * up;
+                        }
+                    } else {
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) {
+                            const float g = __bfloat162float(__float2bfloat16_rn(v[i]));
+                            const float up = __bfloat162float(__float2bfloat16_rn(u[i]));
+                            v[i] = activate(g, p.activation) * up;
+                        }
                     }
                 }
                 if (EPI == kTcActivation) {
@@ -549,7 +567,7 @@ using namespace celeg_b200;
 
 // c[m, n] = a[m, k] * b[n, k]^T in bfloat16 with float32 accumulation on tcgen05 tensor cores.
 // epilogue 0: c bfloat16; 1: c float32; 2: b holds n gate rows then n up rows, c bfloat16 [m, n] =
-// silu(a gate^T) * (a up^T); 3, 4, 5: c bfloat16 = act(a b^T) with the exact GELU, the tanh GELU, SiLU. k, lda and ldb must be multiples of 8 (16-byte rows for TMA); operands
+// silu(a gate^T) * (a up^T) (16 + kind: the same with activate(., kind) on the gate); 3, 4, 5: c bfloat16 = act(a b^T) with the exact GELU, the tanh GELU, SiLU. k, lda and ldb must be multiples of 8 (16-byte rows for TMA); operands
 // 16-byte aligned. error_flag (device int) receives a code if a bounded wait inside the kernel ran out.
 // forced_variant: -1 = the kernel is chosen from the shape, 0..3 = that one (for measurements).
 CELEG_API int celeg_gemm_tcgen05(const void* a, int lda, const void* b, int ldb, void* c, int ldc, int m, int n, int k,
@@ -559,6 +577,12 @@ CELEG_API int celeg_gemm_tcgen05(const void* a, int lda, const void* b, int ldb,
                   "gemm_tcgen05: k=%d, lda=%d and ldb=%d must be multiples of 8 and cover k", k, lda, ldb);
     CELEG_REQUIRE((((size_t)a | (size_t)b) & 15) == 0, "gemm_tcgen05: operands must be 16-byte aligned");
     CELEG_REQUIRE(ldc >= n && error_flag != nullptr, "gemm_tcgen05: ldc=%d is smaller than n=%d, or no error flag", ldc, n);
+    // 16 + kind: the gated form with activate(gate, kind) in place of SiLU
+    int gate_activation = kSilu;
+    if (epilogue >= 16 && epilogue <= 16 + kRelu) {
+        gate_activation = epilogue - 16;
+        epilogue = kTcSwiGlu;
+    }
     CELEG_REQUIRE(epilogue >= 0 && epilogue <= 6, "gemm_tcgen05: unknown epilogue %d", epilogue);
     CELEG_REQUIRE((m + kTileM - 1) / kTileM <= 65535, "gemm_tcgen05: %d rows exceed one launch", m);
     // Which kernel: many rows -> the persistent kernel (128 x 256 tiles, epilogue hidden under the next
@@ -571,7 +595,9 @@ CELEG_API int celeg_gemm_tcgen05(const void* a, int lda, const void* b, int ldb,
     if (!tensor_map_for(a, m, k, lda, kTileM, &map_a)) return -3;
     const long long b_rows = epilogue == kTcSwiGlu ? 2ll * n : n;
     if (!tensor_map_for(b, b_rows, k, ldb, epilogue == kTcSwiGlu ? bn / 2 : bn, &map_b)) return -3;
-    TcGemmParams p{m, n, k, c, ldc, error_flag, epilogue >= kTcActivation ? epilogue - kTcActivation : 0, nullptr, 0};
+    TcGemmParams p{m, n, k, c, ldc, error_flag,
+                   epilogue >= kTcActivation ? epilogue - kTcActivation : (epilogue == kTcSwiGlu ? gate_activation : 0),
+                   nullptr, 0};
     if (epilogue > kTcActivation) epilogue = kTcActivation;
 #define CELEG_TC_DISPATCH(BN, STAGES)                                                        \
     switch (epilogue) {                                                                      \

@@ -613,6 +613,7 @@ def gemv_bf16(x, w: torch.Tensor, y: torch.Tensor, rows: int, mode: int = GEMV_S
 
 TC_STORE, TC_STORE_F32, TC_SWIGLU = 0, 1, 2
 TC_ACTIVATION = 3          # + ACT_GELU_ERF, ACT_GELU_TANH or ACT_SILU: y bfloat16 = act(x w^T)
+TC_GATED = 16              # + a code of ACT_*: as TC_SWIGLU with that function of the gate in place of SiLU
 
 
 def gemm_tcgen05_supported(x: torch.Tensor, w: torch.Tensor) -> bool:
@@ -624,9 +625,10 @@ def gemm_tcgen05(x: torch.Tensor, w: torch.Tensor, y: torch.Tensor, rows: int, e
                  error_flag: torch.Tensor, variant: int = -1) -> None:
     """y[:rows] = x[:rows] @ w.T on tcgen05 tensor cores (TMA-fed, accumulator in tensor memory).
     TC_STORE: y bfloat16; TC_STORE_F32: y float32; TC_SWIGLU: w is [2*inner, k] (gate rows, then up rows),
-    y bfloat16 [rows, inner] = silu(gate) * up. ``variant``: -1 lets the library choose the tile shape,
+    y bfloat16 [rows, inner] = silu(gate) * up; TC_GATED + kind: the same with another function of the gate.
+    ``variant``: -1 lets the library choose the tile shape,
     0..3 force one (128x128 with 6 or 3 stages, 128x256, persistent with two accumulators)."""
-    n = w.shape[0] // 2 if epilogue == TC_SWIGLU else w.shape[0]
+    n = w.shape[0] // 2 if epilogue == TC_SWIGLU or epilogue >= TC_GATED else w.shape[0]
     k = w.shape[1]
     want = torch.float32 if epilogue == TC_STORE_F32 else torch.bfloat16
     if y.dtype != want:

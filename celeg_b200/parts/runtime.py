@@ -298,7 +298,7 @@ class Runtime:
                       out: torch.Tensor, rows: int, inner: int, kind: int = kernels.ACT_SILU) -> None:
         """out[:rows] = act(x gate^T) * (x up^T) with gate_up_weight = [gate rows; up rows], act = SiLU or the
         ``kind`` given (a code of kernels.ACT_*). Few bfloat16 rows: one weight-streaming kernel; very many
-        bfloat16 rows and SiLU: one tcgen05 kernel; otherwise the product into ``scratch`` and the element-wise
+        bfloat16 rows: one tcgen05 kernel (the gate's function in its epilogue); otherwise the product into ``scratch`` and the element-wise
         kernel."""
         if rows == 0:
             return
@@ -307,19 +307,19 @@ class Runtime:
             kernels.gemv_bf16(x, gate_up_weight, out, rows, kernels.GEMV_SWIGLU, ahead=self._ahead(gate_up_weight),
                               taps=0 if kind == kernels.ACT_SILU else 1 + kind)
             return
-        if kind != kernels.ACT_SILU:
-            self.linear(x, gate_up_weight, scratch, rows)
-            kernels.glu(scratch, out, rows, inner, kind)
-            return
         if (self.act_dtype == torch.bfloat16 and kernels.gemm_tcgen05_supported(x, gate_up_weight)
                 and (self.tensor_core_products == "all"
                      or (self.tensor_core_products == "swiglu" and rows >= self.tensor_core_min_rows
                          and gate_up_weight.shape[1] >= self.tensor_core_min_width))):
-            kernels.gemm_tcgen05(x, gate_up_weight, out, rows, kernels.TC_SWIGLU, self.error_flag,
-                                 self.tensor_core_variant)
+            kernels.gemm_tcgen05(x, gate_up_weight, out, rows,
+                                 kernels.TC_SWIGLU if kind == kernels.ACT_SILU else kernels.TC_GATED + kind,
+                                 self.error_flag, self.tensor_core_variant)
             return
         self.linear(x, gate_up_weight, scratch, rows)
-        kernels.swiglu(scratch, out, rows, inner)
+        if kind != kernels.ACT_SILU:
+            kernels.glu(scratch, out, rows, inner, kind)
+        else:
+            kernels.swiglu(scratch, out, rows, inner)
 
     def linear_activation(self, x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, rows: int, kind: int) -> None:
         """out[:rows] = act(x[:rows] @ weight.T), ``kind`` one of kernels.ACT_*. Few bfloat16 rows: the

@@ -366,3 +366,31 @@ def test_per_head_product_with_a_gate_per_element(dtype, rel):
     k.head_project(gpu(x, dtype), kk + 4, gpu(matrix, dtype), False, out, n, tokens, heads, n, kk, gate=gpu(per_head, dtype))
     want = np.einsum("thk,hnk->thn", read, matrix.reshape(heads, n, kk)) * sigmoid(per_head)[:, :, None]
     close(out, want.reshape(tokens, heads * n), rel, "per-head product with a gate per head")
+
+
+# ------------------------------------------------------------------- the gated product on the tcgen05 tensor cores
+@pytest.mark.parametrize("variant", [-1, 1, 3])
+@pytest.mark.parametrize("rows,k,inner", [(300, 64, 128), (700, 256, 384), (129, 72, 40)])
+def test_gated_product_with_another_gate_function_on_tcgen05(rows, k, inner, variant):
+    """[gate | up] in one tcgen05 product with the tanh form of GELU, and with ReLU, on the gate in the epilogue; SiLU
+    through the same code still gives what the SwiGLU epilogue gave."""
+    kn = kernels()
+    rng = np.random.default_rng(rows + k)
+    x = torch.as_tensor(rng.normal(size=(rows, k)), dtype=torch.float32).to(torch.bfloat16).to(DEVICE)
+    w = torch.as_tensor(rng.normal(size=(2 * inner, k)) / math.sqrt(k), dtype=torch.float32).to(torch.bfloat16).to(DEVICE)
+    flag = torch.zeros(1, dtype=torch.int32, device=DEVICE)
+    ref = x.double() @ w.double().t()
+    g = ref[:, :inner].to(torch.bfloat16).double()
+    u = ref[:, inner:].to(torch.bfloat16).double()
+    gates = {kn.ACT_GELU_TANH: 0.5 * g * (1 + torch.tanh(math.sqrt(2 / math.pi) * (g + 0.044715 * g ** 3))),
+             kn.ACT_RELU: torch.clamp(g, min=0.0), kn.ACT_SILU: g / (1 + torch.exp(-g))}
+    for kind, gate in gates.items():
+        out = torch.zeros((rows, inner), dtype=torch.bfloat16, device=DEVICE)
+        kn.gemm_tcgen05(x, w, out, rows, kn.TC_GATED + kind, flag, variant)
+        want = gate * u
+        bad = ((out.double() - want).abs() > 2.5e-2 * (1 + want.abs())).sum().item()
+        assert bad <= rows * inner // 2000, (kind, bad)          # a gate on a rounding edge may flip
+    plain = torch.zeros((rows, inner), dtype=torch.bfloat16, device=DEVICE)
+    kn.gemm_tcgen05(x, w, plain, rows, kn.TC_SWIGLU, flag, variant)
+    assert torch.equal(plain, out)                              # (the last kind above was SiLU)
+    assert int(flag.item()) == 0
