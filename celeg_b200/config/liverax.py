@@ -101,7 +101,10 @@ class LiveraxLayer:
         heads = _positive_int(mixer, "heads", at)
         dim = _positive_int(mixer, "dim", at)
         vdim = _positive_int(mixer, "vdim", at) if mixer.get("vdim") is not None else dim
-        common = dict(type=kind, heads=heads, dim=dim, vdim=vdim, scale=float(_need(mixer, "scale", at)), ff=ff)
+        # (a configuration that leaves the scale out gets one over the root of a key's size)
+        key_size = dim + (_positive_int(mixer, "rot_dim", at) if kind == LATENT_ATTENTION else 0)
+        scale = float(mixer["scale"]) if mixer.get("scale") is not None else key_size ** -0.5
+        common = dict(type=kind, heads=heads, dim=dim, vdim=vdim, scale=scale, ff=ff)
         if kind == LATENT_ATTENTION:
             rot_dim = _positive_int(mixer, "rot_dim", at)
             return LiveraxLayer(**common, rot_dim=rot_dim, kv_rank=_positive_int(mixer, "kv_rank", at),
