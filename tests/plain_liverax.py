@@ -163,10 +163,9 @@ def distance_attention(h: np.ndarray, positions: Sequence[int], m: dict, w: Dict
         shared.setdefault("first_values", v)
     table = w[prefix + "rel"]                                   # [buckets, heads]
     buckets = table.shape[0]
-    rows = np.zeros((tokens, tokens), dtype=np.int64)
-    for i in range(tokens):
-        for j in range(i + 1):
-            rows[i, j] = distance_bucket(positions[i] - positions[j], buckets, m["bias_max"])
+    where = np.asarray(positions, dtype=np.int64)
+    row_of = np.array([distance_bucket(n, buckets, m["bias_max"]) for n in range(int(where.max()) + 1)], dtype=np.int64)
+    rows = row_of[np.clip(where[:, None] - where[None, :], 0, None)]          # (keys after the query are never read)
     mixed = grouped_attention(q, k, v, m["scale"], None, bias_of=lambda head: table[rows, head])
     gate = sigmoid(h @ w[prefix + "g"].T)
     return (mixed * gate) @ w[prefix + "o"].T

@@ -575,3 +575,35 @@ def test_the_trace_runner_as_a_program(models, tmp_path):
     want = plain.forward(raw, tensors, tokens)
     got = np.concatenate([np.fromfile(os.path.join(out_dir, f"{n}.f32"), dtype="<f4").reshape(-1, raw["vocab"]) for n in (0, 2)])
     check(got, want[[0, 17, 20]], "float32", "the program's logits")
+
+
+# ------------------------------------------------------------------------------- layers of a real model's size
+@pytest.fixture(scope="module")
+def large(tmp_path_factory):
+    """Three layers 1,536 wide: 24 query heads of 64 on 6 key heads under a window of 700 with a gated feed-forward of
+    4,096; as many heads with biases by distance in 32 buckets up to 1,024 positions, blended values and no feed-forward;
+    12 latent heads of 64 + 64 over a cached vector of 192 + 64 behind a query latent of 384, under a window of 512. The
+    sizes at which the tcgen05 attention, the tensor-core decode attention, the batched latent products and, from
+    2,048 rows on, the tcgen05 gated product with its GELU epilogue are the ones that run."""
+    raw = lm.config(4096, 1536, [
+        lm.with_mlp(lm.attention(24, 6, 64, 64, window=700, divide=2.0, base=500000.0, v_mix=True), 4096),
+        lm.with_mlp(lm.attention_2(24, 6, 64, 64, 32, 1024, scale=0.1, temp=(0.2, 512), v_mix=True), None),
+        lm.with_mlp(lm.latent(12, 64, 64, 64, 192, 384, window=512), 2048),
+    ])
+    folder = str(tmp_path_factory.mktemp("liverax_large") / "model")
+    disk, bf16 = lm.write_model(folder, raw, 91)
+    tensors = plain.as_float64(bf16)
+    first, second = tokens_of(raw["vocab"], 2130, 500), tokens_of(raw["vocab"], 450, 501)
+    return folder, disk, {"a": first, "b": second}, {"a": plain.forward(disk, tensors, first), "b": plain.forward(disk, tensors, second)}
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_layers_of_a_real_model_size(large, dtype):
+    folder, raw, requests, want = large
+    first, second = requests["a"], requests["b"]
+    loaded = load(folder, dtype, cache_tokens=4096, max_batched_tokens=2560, max_context=4096)
+    steps = [[("a", first[:2100])], [("a", first[2100:2101]), ("b", second[:300])], [("a", first[2101:2102]), ("b", second[300:])]]
+    steps += [[("a", [t])] for t in first[2102:]]
+    got = run_steps(loaded, steps)
+    for key in ("a", "b"):
+        check(got[key], want[key], dtype, f"request {key} at a real model's layer sizes")
