@@ -20,7 +20,7 @@ from .ramosun import DEFAULT_MAX_CONTEXT, _need
 
 
 def _positive_int(mapping: Mapping[str, Any], key: str, where: str) -> int:
-    """A count; a JSON writer may have left a whole number as 240.0."""
+    """A count; a JSON writer may have left a whole number as 64.0."""
     value = _need(mapping, key, where)
     if isinstance(value, float) and value.is_integer():
         value = int(value)
